@@ -1,0 +1,173 @@
+"""Generate the golden fixtures in this directory by running the reference itself.
+
+Usage (only where the reference checkout is mounted; the fixtures are committed so
+nothing at test time needs it):
+
+    python tests/golden/make_golden.py /path/to/reference
+
+The reference package imports ``matplotlib`` unconditionally (``src/qkan/qkan.py:33``)
+for its plotting helpers; an empty stand-in module is registered before the import,
+which does not touch any arithmetic.
+
+What is written:
+
+* ``layer_cases.npz`` — for a grid of small ``QKANLayer`` configurations run with the
+  reference ``exact`` solver in complex128/float64: the inputs, ``y``, the per-edge
+  ``postacts`` and every gradient of ``sum(y * gy)`` from torch autograd; plus ``y`` from
+  the reference's default complex64/float32 arithmetic.
+* ``init_cases.npz`` — seeded parameter initialisations (``state_dict`` tensors).
+* ``fit_case.npz`` — the 1-D function-fit configuration: dataset, seeded initial
+  prediction / loss / gradients, and the LBFGS loss trajectory of the reference.
+"""
+from __future__ import annotations
+
+import os
+import sys
+import types
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+# name, B, I, O, R, preact_trainable, fast_measure, postact_bias, base, masked
+LAYER_CASES = [
+    ("tiny_1x1", 9, 1, 1, 3, True, True, True, True, False),
+    ("r1_fast", 5, 3, 4, 1, True, True, False, False, False),
+    ("r2_born", 6, 4, 3, 2, True, False, True, False, False),
+    ("r3_fixed_preact", 7, 5, 2, 3, False, True, False, True, False),
+    ("r3_all", 8, 3, 5, 3, True, True, True, True, True),
+    ("r4_fixed_born", 4, 2, 3, 4, False, False, True, False, True),
+    ("r8_fast", 3, 2, 2, 8, True, True, False, False, False),
+    ("wide_in", 4, 37, 3, 2, True, True, True, False, True),
+    ("wide_out", 4, 3, 41, 2, False, True, False, True, False),
+    ("r5_mixed", 5, 6, 7, 5, True, True, True, True, True),
+]
+
+
+def _import_reference(ref_root: str):
+    for name in ("matplotlib", "matplotlib.pyplot"):
+        sys.modules.setdefault(name, types.ModuleType(name))
+    sys.modules["matplotlib"].pyplot = sys.modules["matplotlib.pyplot"]
+    sys.path.insert(0, os.path.join(ref_root, "src"))
+    import qkan  # noqa: F401
+
+    return qkan
+
+
+def layer_cases(qkan, torch):
+    out = {}
+    for idx, (name, B, I, O, R, ptr, fast, use_pb, base, masked) in enumerate(LAYER_CASES):
+        g = torch.Generator().manual_seed(1000 + idx)
+        rnd = lambda *s: torch.rand(*s, generator=g, dtype=torch.float64)  # noqa: E731
+        nrm = lambda *s: torch.randn(*s, generator=g, dtype=torch.float64)  # noqa: E731
+        inp = {
+            "x": rnd(B, I) * 4 - 2,
+            "theta": (rnd(O, I, R + 1, 2) * 2 - 1) * np.pi,
+            "preacts_weight": 1 + 0.3 * nrm(O, I, R),
+            "preacts_bias": 0.3 * nrm(O, I, R),
+            "postact_weights": nrm(O, I) / np.sqrt(I),
+            "postact_bias": 0.5 * nrm(O, I) if use_pb else torch.zeros(O, I, dtype=torch.float64),
+            "base_weight": 0.5 * nrm(O, I) if base else torch.zeros(O, I, dtype=torch.float64),
+            "mask": (rnd(O, I) > 0.3).double() if masked else torch.ones(O, I, dtype=torch.float64),
+            "gy": nrm(B, O),
+        }
+        flags = dict(preact_trainable=ptr, fast_measure=fast, use_postact_bias=use_pb, base=base,
+                     masked=masked)
+        for prec, cd, pd in (("f64", torch.complex128, torch.float64), ("f32", torch.complex64, torch.float32)):
+            layer = qkan.QKANLayer(I, O, reps=R, solver="exact", preact_trainable=ptr,
+                                   postact_weight_trainable=True, postact_bias_trainable=use_pb,
+                                   ba_trainable=base, fast_measure=fast, c_dtype=cd, p_dtype=pd)
+            with torch.no_grad():
+                for pname in ("theta", "preacts_weight", "preacts_bias", "postact_weights",
+                              "postact_bias", "base_weight", "mask"):
+                    getattr(layer, pname).data.copy_(inp[pname].to(pd))
+            layer._mask_is_identity = not masked
+            layer.train()
+            x = inp["x"].to(pd).clone().requires_grad_(True)
+            y = layer(x)
+            if prec == "f32":
+                out[f"{name}/y_f32"] = y.detach().numpy()
+                continue
+            (y * inp["gy"]).sum().backward()
+            out[f"{name}/y"] = y.detach().numpy()
+            solver = qkan.solver.get_solver("exact")
+            with torch.no_grad():
+                pa = solver(x.detach(), layer.theta, layer.preacts_weight, layer.preacts_bias, R,
+                            ansatz="pz_encoding", preacts_trainable=ptr, fast_measure=fast,
+                            out_dim=O, dtype=cd)
+            out[f"{name}/postacts"] = pa.numpy()
+            out[f"{name}/g_x"] = x.grad.numpy()
+            for pname in ("theta", "preacts_weight", "preacts_bias", "postact_weights",
+                          "postact_bias", "base_weight"):
+                grad = getattr(layer, pname).grad
+                out[f"{name}/g_{pname}"] = (grad.numpy() if grad is not None
+                                            else np.zeros(tuple(getattr(layer, pname).shape)))
+        for k, v in inp.items():
+            out[f"{name}/in_{k}"] = v.numpy()
+        out[f"{name}/flags"] = np.array([int(flags[k]) for k in
+                                         ("preact_trainable", "fast_measure", "use_postact_bias",
+                                          "base", "masked")], dtype=np.int64)
+        out[f"{name}/dims"] = np.array([B, I, O, R], dtype=np.int64)
+    out["names"] = np.array([c[0] for c in LAYER_CASES])
+    np.savez_compressed(os.path.join(HERE, "layer_cases.npz"), **out)
+
+
+def init_cases(qkan, torch):
+    out = {}
+    specs = {
+        "fit_1_1": dict(width=[1, 1], reps=3, seed=0),
+        "mlp_3_4_2": dict(width=[3, 4, 2], reps=2, seed=7, preact_trainable=True, preact_init=True),
+        "pdim2": dict(width=[5, 3], reps=3, seed=3, p_dim=2, ba_trainable=True),
+        "map_head": dict(width=[4, 3, 6, 2], reps=1, seed=11, is_map=True, hidden=6),
+        "bn_small_gauss": dict(width=[3, 2], reps=2, seed=5, is_batchnorm=True, theta_init="small_gaussian"),
+    }
+    for name, kw in specs.items():
+        model = qkan.QKAN(**kw)
+        for k, v in model.state_dict().items():
+            out[f"{name}/{k}"] = v.detach().numpy()
+    layer = qkan.QKANLayer(4, 3, reps=2, seed=1)
+    for k, v in layer.state_dict().items():
+        out[f"layer_4_3/{k}"] = v.detach().numpy()
+    np.savez_compressed(os.path.join(HERE, "init_cases.npz"), **out)
+
+
+def fit_case(qkan, torch):
+    f = lambda x: torch.sin(20 * x) / (20 * x)  # noqa: E731
+    dataset = qkan.create_dataset(f, n_var=1, ranges=[0, 1], train_num=1000, test_num=1000, seed=0)
+    out = {k: v.numpy() for k, v in dataset.items()}
+    for tag, ba in (("ba", True), ("noba", False)):
+        model = qkan.QKAN([1, 1], reps=3, seed=0, preact_trainable=True, postact_weight_trainable=True,
+                          postact_bias_trainable=True, ba_trainable=ba)
+        model.train()
+        pred = model(dataset["train_input"])
+        loss = torch.nn.functional.mse_loss(pred, dataset["train_label"])
+        loss.backward()
+        out[f"{tag}/pred0"] = pred.detach().numpy()
+        out[f"{tag}/loss0"] = np.array(loss.item())
+        for k, p in model.named_parameters():
+            if p.grad is not None:
+                out[f"{tag}/grad/{k}"] = p.grad.numpy().copy()
+        model.zero_grad()
+        opt = torch.optim.LBFGS(model.parameters(), lr=5e-2)
+        res = model.train_(dataset, optimizer=opt, steps=100, verbose=False)
+        out[f"{tag}/train_loss"] = np.array([float(v) for v in res["train_loss"]])
+        out[f"{tag}/test_loss"] = np.array([float(v) for v in res["test_loss"]])
+    np.savez_compressed(os.path.join(HERE, "fit_case.npz"), **out)
+
+
+def main():
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("QKAN_REFERENCE_ROOT", "")
+    if not ref_root or not os.path.isdir(ref_root):
+        raise SystemExit("usage: make_golden.py <reference checkout>")
+    import torch
+
+    torch.set_num_threads(max(1, os.cpu_count() or 1))
+    qkan = _import_reference(ref_root)
+    layer_cases(qkan, torch)
+    init_cases(qkan, torch)
+    fit_case(qkan, torch)
+    print("wrote", sorted(p for p in os.listdir(HERE) if p.endswith(".npz")))
+
+
+if __name__ == "__main__":
+    main()
