@@ -1,0 +1,123 @@
+/*
+ * qkan_b200 — C ABI of the sm_100a QKANLayer kernels (pz_encoding ansatz).
+ *
+ * Every entry point takes plain device pointers and sizes, launches on the
+ * stream it is given, never synchronises, never allocates and never throws.
+ * Return value: 0 on success, a negative QK_ERR_* code otherwise;
+ * qk_last_error() then returns a thread-local description.
+ *
+ * Tensor layouts are the reference's natural-rank, row-major layouts
+ * (src/qkan/qkan.py:259-347):
+ *   x (B,I)  y (B,O)  theta (O,I,R+1,2)  preacts_weight/bias (O,I,R)
+ *   postact_weights / postact_bias / base_weight / mask (O,I)
+ * theta and preacts are always float32. x, y and their gradients use
+ * QkDesc.io_dtype; the four (O,I) tensors use QkDesc.param_dtype. All
+ * gradient outputs of parameters are float32.
+ */
+#ifndef QKAN_B200_H_
+#define QKAN_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define QK_ABI_VERSION 1
+
+enum QkDtype { QK_F32 = 0, QK_BF16 = 1 };
+
+enum QkFlags {
+    QK_PREACT_TRAINABLE = 1u, /* encode pw*x+pb; otherwise x itself (exact.py:87,121-124) */
+    QK_FAST_MEASURE = 2u,     /* |a|-|b| readout; otherwise |a|^2-|b|^2 (torch_qc.py:261-277) */
+    QK_USE_POSTACT_BIAS = 4u  /* add postact_bias before the weight (qkan.py:776-783) */
+};
+
+enum QkError {
+    QK_OK = 0,
+    QK_ERR_BAD_ARGUMENT = -1,
+    QK_ERR_UNSUPPORTED = -2,
+    QK_ERR_WORKSPACE = -3,
+    QK_ERR_LAUNCH = -4
+};
+
+typedef struct QkDesc {
+    int32_t batch;       /* B */
+    int32_t in_dim;      /* I */
+    int32_t out_dim;     /* O */
+    int32_t reps;        /* R >= 1 */
+    int32_t io_dtype;    /* QkDtype of x, y, grad_y, grad_x */
+    int32_t param_dtype; /* QkDtype of postact_weights, postact_bias, base_weight, mask */
+    uint32_t flags;      /* QkFlags */
+    int32_t reserved;    /* must be 0 */
+} QkDesc;
+
+/* ABI version of the loaded library (compare with QK_ABI_VERSION). */
+int qk_abi_version(void);
+
+/* Thread-local text of the last error returned on this thread ("" if none). */
+const char* qk_last_error(void);
+
+/*
+ * Bytes of device scratch the forward / backward need for this problem.
+ * The caller owns the scratch (any 256-byte aligned device allocation) and
+ * may reuse it between calls on the same stream.
+ */
+size_t qk_forward_workspace_bytes(const QkDesc* desc);
+size_t qk_backward_workspace_bytes(const QkDesc* desc);
+
+/*
+ * Fused layer forward: replaces the body of QKANLayer._forward_train /
+ * _forward_eval after the optional batch-norm (src/qkan/qkan.py:727-785):
+ * solver call (src/qkan/solver/exact.py:90-134) + mask fold + epilogue
+ *   y[b,o] = sum_i (postacts[b,o,i] + postact_bias[o,i]) * postact_weights[o,i] * mask[o,i]
+ *          + sum_i silu(x[b,i]) * base_weight[o,i] * mask[o,i]
+ * without materialising postacts. postact_bias, base_weight and mask may be
+ * NULL (zero, zero, ones).
+ */
+int qk_pz_forward(const QkDesc* desc, const void* x, const float* theta,
+                  const float* preacts_weight, const float* preacts_bias,
+                  const void* postact_weights, const void* postact_bias, const void* base_weight,
+                  const void* mask, void* y, void* workspace, size_t workspace_bytes,
+                  void* cuda_stream);
+
+/*
+ * Fused layer backward: what torch autograd derives for the reference's
+ * exact solver plus epilogue (src/qkan/solver/exact.py:90-134,
+ * src/qkan/qkan.py:776-785; the fused reference counterparts are
+ * src/qkan/csrc/cute_kernels.cu:216-508 and src/qkan/qkan_epilogue.py:187-309).
+ * Every gradient pointer may be NULL when that gradient is not wanted.
+ * Parameter gradients are summed over the batch in a fixed order
+ * (run-to-run bitwise reproducible) and are OVERWRITTEN, not accumulated.
+ */
+int qk_pz_backward(const QkDesc* desc, const void* x, const float* theta,
+                   const float* preacts_weight, const float* preacts_bias,
+                   const void* postact_weights, const void* postact_bias, const void* base_weight,
+                   const void* mask, const void* grad_y, void* grad_x, float* grad_theta,
+                   float* grad_preacts_weight, float* grad_preacts_bias,
+                   float* grad_postact_weights, float* grad_postact_bias, float* grad_base_weight,
+                   void* workspace, size_t workspace_bytes, void* cuda_stream);
+
+/*
+ * Solver plug-in contract (src/qkan/solver/_base.py:29-51, call site
+ * src/qkan/qkan.py:699-714): per-edge activations postacts (B,O,I) in
+ * io_dtype, and the matching backward from grad_postacts (B,O,I). Used by
+ * forward_no_sum / save_act (src/qkan/qkan.py:835-891, 1280-1302) and when
+ * the kernels are registered as a solver inside the reference's own layer.
+ */
+int qk_pz_postacts_forward(const QkDesc* desc, const void* x, const float* theta,
+                           const float* preacts_weight, const float* preacts_bias,
+                           void* postacts, void* workspace, size_t workspace_bytes,
+                           void* cuda_stream);
+
+int qk_pz_postacts_backward(const QkDesc* desc, const void* x, const float* theta,
+                            const float* preacts_weight, const float* preacts_bias,
+                            const void* grad_postacts, void* grad_x, float* grad_theta,
+                            float* grad_preacts_weight, float* grad_preacts_bias,
+                            void* workspace, size_t workspace_bytes, void* cuda_stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* QKAN_B200_H_ */

@@ -1,0 +1,309 @@
+// C ABI of the library (see include/qkan_b200.h): argument validation,
+// workspace carving and the kernel launch sequence. No torch types, no
+// allocation, no synchronisation.
+#include <cstdarg>
+#include <cstdio>
+
+#include "qk_kernels.cuh"
+
+namespace {
+
+thread_local char g_err[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+int check_desc(const QkDesc* d) {
+    if (!d) return fail(QK_ERR_BAD_ARGUMENT, "desc is NULL");
+    if (d->batch < 0 || d->in_dim < 0 || d->out_dim < 0)
+        return fail(QK_ERR_BAD_ARGUMENT, "negative dimension (B=%d I=%d O=%d)", d->batch, d->in_dim,
+                    d->out_dim);
+    if (d->reps < 1) return fail(QK_ERR_BAD_ARGUMENT, "reps must be >= 1 (got %d)", d->reps);
+    if (d->reps > qk::kMaxRepsTemplated)
+        return fail(QK_ERR_UNSUPPORTED, "reps=%d exceeds the compiled maximum of %d", d->reps,
+                    qk::kMaxRepsTemplated);
+    if (d->io_dtype != QK_F32 && d->io_dtype != QK_BF16)
+        return fail(QK_ERR_BAD_ARGUMENT, "io_dtype %d is neither QK_F32 nor QK_BF16", d->io_dtype);
+    if (d->param_dtype != QK_F32 && d->param_dtype != QK_BF16)
+        return fail(QK_ERR_BAD_ARGUMENT, "param_dtype %d is neither QK_F32 nor QK_BF16",
+                    d->param_dtype);
+    if (d->flags & ~(QK_PREACT_TRAINABLE | QK_FAST_MEASURE | QK_USE_POSTACT_BIAS))
+        return fail(QK_ERR_BAD_ARGUMENT, "unknown flag bits 0x%x", d->flags);
+    if (d->reserved != 0) return fail(QK_ERR_BAD_ARGUMENT, "reserved field must be 0");
+    if ((long long)d->out_dim > 65535)
+        return fail(QK_ERR_UNSUPPORTED, "out_dim %d exceeds 65535", d->out_dim);
+    return QK_OK;
+}
+
+struct Layout {
+    int ipad;
+    size_t table_off, bias_off, colsum_off, partials_off, total;
+    int ncolsplit;
+};
+
+Layout forward_layout(const QkDesc& d) {
+    Layout l{};
+    l.ipad = qk::round_up(d.in_dim, 32);
+    l.table_off = 0;
+    size_t table = (size_t)d.out_dim * qk::table_rows(d.reps) * l.ipad * sizeof(float);
+    l.bias_off = qk::align256(table);
+    l.total = l.bias_off + qk::align256((size_t)d.out_dim * sizeof(float));
+    return l;
+}
+
+Layout backward_layout(const QkDesc& d, bool base) {
+    Layout l = forward_layout(d);
+    qk::BwdCfg c = qk::choose_bwd_cfg(d, base);
+    l.ncolsplit = d.batch <= 0 ? 1 : (d.batch + 255) / 256;
+    if (l.ncolsplit > 64) l.ncolsplit = 64;
+    l.colsum_off = l.total;
+    l.partials_off = l.colsum_off + qk::align256((size_t)l.ncolsplit * d.out_dim * sizeof(float));
+    l.total = l.partials_off +
+              qk::align256((size_t)c.grid_b * d.out_dim * c.nacc * l.ipad * sizeof(float));
+    return l;
+}
+
+bool empty(const QkDesc& d) { return d.batch == 0 || d.in_dim == 0 || d.out_dim == 0; }
+
+int cuda_fail(cudaError_t e, const char* what) {
+    return fail(QK_ERR_LAUNCH, "%s: %s", what, cudaGetErrorString(e));
+}
+
+int run_forward(const QkDesc* desc, const void* x, const float* theta, const float* pw,
+                const float* pb, const void* postw, const void* postb, const void* basew,
+                const void* mask, void* y, void* postacts, void* ws, size_t ws_bytes,
+                cudaStream_t st) {
+    int rc = check_desc(desc);
+    if (rc) return rc;
+    const QkDesc& d = *desc;
+    const bool edges = postacts != nullptr;
+    if (empty(d)) {
+        // y (B,O) of an in_dim == 0 layer is all zeros; the other empty shapes have no output
+        if (!edges && d.in_dim == 0 && d.batch > 0 && d.out_dim > 0) {
+            size_t es = d.io_dtype == QK_BF16 ? 2 : 4;
+            cudaError_t e = cudaMemsetAsync(y, 0, (size_t)d.batch * d.out_dim * es, st);
+            if (e != cudaSuccess) return cuda_fail(e, "memset y");
+        }
+        return QK_OK;
+    }
+    if (!x || !theta || !pw || !pb) return fail(QK_ERR_BAD_ARGUMENT, "x/theta/preacts pointer is NULL");
+    if (!edges && (!postw || !y)) return fail(QK_ERR_BAD_ARGUMENT, "postact_weights or y is NULL");
+    Layout l = forward_layout(d);
+    if (!ws || ws_bytes < l.total)
+        return fail(QK_ERR_WORKSPACE, "workspace too small: need %zu bytes, got %zu", l.total, ws_bytes);
+    if ((uintptr_t)ws % 256)
+        return fail(QK_ERR_WORKSPACE, "workspace must be 256-byte aligned");
+    char* wsb = static_cast<char*>(ws);
+    const bool has_base = !edges && basew != nullptr;
+
+    qk::PrepArgs p{};
+    p.in_dim = d.in_dim;
+    p.out_dim = d.out_dim;
+    p.reps = d.reps;
+    p.ipad = l.ipad;
+    p.flags = d.flags;
+    p.param_dtype = d.param_dtype;
+    p.theta = theta;
+    p.pw = pw;
+    p.pb = pb;
+    p.postw = edges ? nullptr : postw;
+    p.postb = edges ? nullptr : postb;
+    p.basew = has_base ? basew : nullptr;
+    p.mask = edges ? nullptr : mask;
+    p.table = reinterpret_cast<float*>(wsb + l.table_off);
+    p.bias = edges ? nullptr : reinterpret_cast<float*>(wsb + l.bias_off);
+    cudaError_t e = qk::launch_prep(p, st);
+    if (e != cudaSuccess) return cuda_fail(e, "prep launch");
+
+    qk::FwdArgs f{};
+    f.batch = d.batch;
+    f.in_dim = d.in_dim;
+    f.out_dim = d.out_dim;
+    f.ipad = l.ipad;
+    f.cfg = qk::choose_fwd_cfg(d, edges, has_base);
+    f.x = x;
+    f.table = p.table;
+    f.bias = p.bias;
+    f.y = y;
+    f.postacts = postacts;
+    e = qk::launch_forward(f, d.reps, (d.flags & QK_FAST_MEASURE) != 0, d.io_dtype, has_base, st);
+    if (e != cudaSuccess) return cuda_fail(e, "forward launch");
+    return QK_OK;
+}
+
+int run_backward(const QkDesc* desc, const void* x, const float* theta, const float* pw,
+                 const float* pb, const void* postw, const void* postb, const void* basew,
+                 const void* mask, const void* gy, const void* gpostacts, void* gx, float* gtheta,
+                 float* gpw, float* gpb, float* gpostw, float* gpostb, float* gbasew, void* ws,
+                 size_t ws_bytes, cudaStream_t st) {
+    int rc = check_desc(desc);
+    if (rc) return rc;
+    const QkDesc& d = *desc;
+    const bool edges = gpostacts != nullptr;
+    const size_t nE = (size_t)d.out_dim * d.in_dim;
+    if (empty(d)) {
+        // no rows (or no edges): every requested gradient is zero
+        cudaError_t e = cudaSuccess;
+        size_t es = d.io_dtype == QK_BF16 ? 2 : 4;
+        if (gx && (size_t)d.batch * d.in_dim) e = cudaMemsetAsync(gx, 0, (size_t)d.batch * d.in_dim * es, st);
+        if (e == cudaSuccess && gtheta && nE) e = cudaMemsetAsync(gtheta, 0, nE * (d.reps + 1) * 2 * 4, st);
+        if (e == cudaSuccess && gpw && nE) e = cudaMemsetAsync(gpw, 0, nE * d.reps * 4, st);
+        if (e == cudaSuccess && gpb && nE) e = cudaMemsetAsync(gpb, 0, nE * d.reps * 4, st);
+        if (e == cudaSuccess && gpostw && nE) e = cudaMemsetAsync(gpostw, 0, nE * 4, st);
+        if (e == cudaSuccess && gpostb && nE) e = cudaMemsetAsync(gpostb, 0, nE * 4, st);
+        if (e == cudaSuccess && gbasew && nE) e = cudaMemsetAsync(gbasew, 0, nE * 4, st);
+        if (e != cudaSuccess) return cuda_fail(e, "memset gradients");
+        return QK_OK;
+    }
+    if (!x || !theta || !pw || !pb) return fail(QK_ERR_BAD_ARGUMENT, "x/theta/preacts pointer is NULL");
+    if (!edges && (!postw || !gy)) return fail(QK_ERR_BAD_ARGUMENT, "postact_weights or grad_y is NULL");
+    const bool has_base = !edges && basew != nullptr;
+    Layout l = backward_layout(d, has_base);
+    if (!ws || ws_bytes < l.total)
+        return fail(QK_ERR_WORKSPACE, "workspace too small: need %zu bytes, got %zu", l.total, ws_bytes);
+    if ((uintptr_t)ws % 256)
+        return fail(QK_ERR_WORKSPACE, "workspace must be 256-byte aligned");
+    char* wsb = static_cast<char*>(ws);
+
+    qk::PrepArgs p{};
+    p.in_dim = d.in_dim;
+    p.out_dim = d.out_dim;
+    p.reps = d.reps;
+    p.ipad = l.ipad;
+    p.flags = d.flags;
+    p.param_dtype = d.param_dtype;
+    p.theta = theta;
+    p.pw = pw;
+    p.pb = pb;
+    p.postw = edges ? nullptr : postw;
+    p.postb = edges ? nullptr : postb;
+    p.basew = has_base ? basew : nullptr;
+    p.mask = edges ? nullptr : mask;
+    p.table = reinterpret_cast<float*>(wsb + l.table_off);
+    p.bias = nullptr;
+    cudaError_t e = qk::launch_prep(p, st);
+    if (e != cudaSuccess) return cuda_fail(e, "prep launch");
+
+    const bool use_pb = !edges && (d.flags & QK_USE_POSTACT_BIAS) && postb;
+    float* colsum = reinterpret_cast<float*>(wsb + l.colsum_off);
+    const bool need_colsum = use_pb && (gpostw || gpostb);
+    if (need_colsum) {
+        e = qk::launch_colsum(gy, d.io_dtype, d.batch, d.out_dim, l.ncolsplit, colsum, st);
+        if (e != cudaSuccess) return cuda_fail(e, "colsum launch");
+    }
+
+    qk::BwdArgs b{};
+    b.batch = d.batch;
+    b.in_dim = d.in_dim;
+    b.out_dim = d.out_dim;
+    b.ipad = l.ipad;
+    b.cfg = qk::choose_bwd_cfg(d, has_base);
+    b.x = x;
+    b.gy = gy;
+    b.gpostacts = gpostacts;
+    b.table = p.table;
+    b.gx = gx;
+    b.partials = reinterpret_cast<float*>(wsb + l.partials_off);
+    e = qk::launch_backward(b, d.reps, (d.flags & QK_FAST_MEASURE) != 0, d.io_dtype, has_base, st);
+    if (e != cudaSuccess) return cuda_fail(e, "backward launch");
+
+    if (gtheta || gpw || gpb || gpostw || gpostb || gbasew) {
+        qk::FinishArgs f{};
+        f.in_dim = d.in_dim;
+        f.out_dim = d.out_dim;
+        f.reps = d.reps;
+        f.ipad = l.ipad;
+        f.nacc = b.cfg.nacc;
+        f.ntiles = b.cfg.grid_b;
+        f.ncolsplit = l.ncolsplit;
+        f.has_base = has_base;
+        f.flags = d.flags;
+        f.param_dtype = d.param_dtype;
+        f.partials = b.partials;
+        f.colsum = need_colsum ? colsum : nullptr;
+        f.postw = edges ? nullptr : postw;
+        f.postb = edges ? nullptr : postb;
+        f.mask = edges ? nullptr : mask;
+        f.gtheta = gtheta;
+        f.gpw = gpw;
+        f.gpb = gpb;
+        f.gpostw = edges ? nullptr : gpostw;
+        f.gpostb = edges ? nullptr : gpostb;
+        f.gbasew = edges ? nullptr : gbasew;
+        e = qk::launch_finish(f, st);
+        if (e != cudaSuccess) return cuda_fail(e, "finish launch");
+    }
+    return QK_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int qk_abi_version(void) { return QK_ABI_VERSION; }
+
+const char* qk_last_error(void) { return g_err; }
+
+size_t qk_forward_workspace_bytes(const QkDesc* desc) {
+    if (check_desc(desc)) return 0;
+    if (empty(*desc)) return 256;
+    return forward_layout(*desc).total;
+}
+
+size_t qk_backward_workspace_bytes(const QkDesc* desc) {
+    if (check_desc(desc)) return 0;
+    if (empty(*desc)) return 256;
+    // sized for the larger of the two accumulator sets so one query covers both modes
+    return backward_layout(*desc, true).total > backward_layout(*desc, false).total
+               ? backward_layout(*desc, true).total
+               : backward_layout(*desc, false).total;
+}
+
+int qk_pz_forward(const QkDesc* desc, const void* x, const float* theta, const float* pw,
+                  const float* pb, const void* postw, const void* postb, const void* basew,
+                  const void* mask, void* y, void* ws, size_t ws_bytes, void* stream) {
+    return run_forward(desc, x, theta, pw, pb, postw, postb, basew, mask, y, nullptr, ws, ws_bytes,
+                       static_cast<cudaStream_t>(stream));
+}
+
+int qk_pz_backward(const QkDesc* desc, const void* x, const float* theta, const float* pw,
+                   const float* pb, const void* postw, const void* postb, const void* basew,
+                   const void* mask, const void* gy, void* gx, float* gtheta, float* gpw,
+                   float* gpb, float* gpostw, float* gpostb, float* gbasew, void* ws,
+                   size_t ws_bytes, void* stream) {
+    return run_backward(desc, x, theta, pw, pb, postw, postb, basew, mask, gy, nullptr, gx, gtheta,
+                        gpw, gpb, gpostw, gpostb, gbasew, ws, ws_bytes,
+                        static_cast<cudaStream_t>(stream));
+}
+
+int qk_pz_postacts_forward(const QkDesc* desc, const void* x, const float* theta, const float* pw,
+                           const float* pb, void* postacts, void* ws, size_t ws_bytes,
+                           void* stream) {
+    if (!postacts && desc && !empty(*desc)) return fail(QK_ERR_BAD_ARGUMENT, "postacts is NULL");
+    if (!postacts) return check_desc(desc);
+    return run_forward(desc, x, theta, pw, pb, nullptr, nullptr, nullptr, nullptr, nullptr, postacts,
+                       ws, ws_bytes, static_cast<cudaStream_t>(stream));
+}
+
+int qk_pz_postacts_backward(const QkDesc* desc, const void* x, const float* theta, const float* pw,
+                            const float* pb, const void* gpostacts, void* gx, float* gtheta,
+                            float* gpw, float* gpb, void* ws, size_t ws_bytes, void* stream) {
+    if (!gpostacts && desc && !empty(*desc)) return fail(QK_ERR_BAD_ARGUMENT, "grad_postacts is NULL");
+    if (!gpostacts) {
+        // empty problem: zero the requested gradients through the common path
+        static const char dummy = 0;
+        return run_backward(desc, x, theta, pw, pb, nullptr, nullptr, nullptr, nullptr, nullptr,
+                            &dummy, gx, gtheta, gpw, gpb, nullptr, nullptr, nullptr, ws, ws_bytes,
+                            static_cast<cudaStream_t>(stream));
+    }
+    return run_backward(desc, x, theta, pw, pb, nullptr, nullptr, nullptr, nullptr, nullptr,
+                        gpostacts, gx, gtheta, gpw, gpb, nullptr, nullptr, nullptr, ws, ws_bytes,
+                        static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,236 @@
+// Fused backward: grad_x and the batch-summed gradients of every per-edge
+// parameter, from recomputed circuit states (nothing is checkpointed).
+// Replaces what autograd derives for the reference's solver + epilogue
+// (src/qkan/solver/exact.py:90-134, src/qkan/qkan.py:776-785; fused reference
+// counterparts: src/qkan/csrc/cute_kernels.cu:216-508 and
+// src/qkan/qkan_epilogue.py:187-309).
+//
+// Mapping: a lane owns one input column i; a CTA owns 32 columns and
+// `groups * rpg` batch rows (one warp per group of rpg rows) and walks every
+// output o. For the current edge (o,i) a thread keeps the edge constants and
+// the 3R+3 gradient accumulators in registers while it runs through its rows,
+// so the sum over the batch needs no cross-lane traffic; grad_x[b,i]
+// accumulates over o in a thread-private shared-memory column. After each o
+// the groups' accumulators are summed through shared memory (block-level
+// reduction) and written as this batch tile's partial; finish_grads then sums
+// the tiles in a fixed order (cross-CTA reduction, bitwise reproducible).
+#include "qk_kernels.cuh"
+
+namespace qk {
+
+__device__ __forceinline__ float sigmoid_f(float v) { return 1.f / (1.f + expf(-v)); }
+
+template <int R, bool FAST, bool BASE, bool EDGES, int NACC>
+__device__ __forceinline__ float edge_backward(const EdgeFwd<R>& e, float bw, float x, float g,
+                                               float sl, float dsl, float (&acc)[NACC]) {
+    float cs[R], sn[R], vx, vy, vz, inv_rho, r;
+    const float p = edge_forward<R, FAST, true>(e, x, cs, sn, vx, vy, vz, inv_rho, r);
+    const float gp = EDGES ? g : g * e.w;
+    if (!EDGES) acc[a_w(R)] = fmaf(g, p, acc[a_w(R)]);
+    // w = v x a, a = cotangent of the final Bloch vector (its z component of w is 0)
+    float wx, wy, wz;
+    if (FAST) {
+        const float az = gp * r;
+        const float t = az * r * r;
+        const float q = (t * vz) * (-0.5f * inv_rho);
+        const float ax = q * vx, ay = q * vy;
+        wx = fmaf(vy, az, -(vz * ay));
+        wy = fmaf(vz, ax, -(vx * az));
+    } else {
+        wx = vy * gp;
+        wy = -(vx * gp);
+    }
+    acc[a_ry(R)] += wy;  // final Ry(theta[R,1])
+    wz = wx * e.sf;
+    wx = wx * e.cf;
+    float gx = 0.f;
+#pragma unroll
+    for (int l = R - 1; l >= 0; --l) {
+        // merged Rz(pw_l x + c_l): its angle gradient is wz
+        acc[a_c(R, l)] += wz;
+        acc[a_pwx(R, l)] = fmaf(wz, x, acc[a_pwx(R, l)]);
+        gx = fmaf(wz, e.pw[l], gx);
+        float nx = fmaf(wy, sn[l], wx * cs[l]);
+        float ny = fmaf(-wx, sn[l], wy * cs[l]);
+        wx = nx;
+        wy = ny;
+        acc[a_ry(l)] += wy;  // Ry(theta[l,1])
+        if (l > 0) {
+            float mx = fmaf(-wz, e.sa[l], wx * e.ca[l]);
+            float mz = fmaf(wx, e.sa[l], wz * e.ca[l]);
+            wx = mx;
+            wz = mz;
+        } else {
+            wz = fmaf(wx, e.sa[0], wz * e.ca[0]);
+        }
+    }
+    acc[a_t00(R)] += wz;  // Rz(theta[0,0])
+    if (BASE) {
+        acc[a_bw(R)] = fmaf(g, sl, acc[a_bw(R)]);
+        gx = fmaf(g * bw, dsl, gx);
+    }
+    return gx;
+}
+
+template <int R, bool FAST, typename IO, bool BASE, bool EDGES, int RU>
+__global__ void __launch_bounds__(512) backward_kernel(BwdArgs a) {
+    constexpr int NACC = acc_rows(R, BASE);
+    extern __shared__ __align__(16) float smem[];
+    const int groups = a.cfg.groups, rpg = a.cfg.rpg, tb = a.cfg.tb;
+    float* x_s = smem;                     // [tb][32]
+    float* gx_s = x_s + (size_t)tb * 32;   // [tb][32]
+    float* sl_s = gx_s + (size_t)tb * 32;  // [tb][32] silu(x)        (BASE)
+    float* dsl_s = sl_s + (BASE ? (size_t)tb * 32 : 0);  // [tb][32] silu'(x) (BASE)
+    float* red_s = dsl_s + (BASE ? (size_t)tb * 32 : 0);  // [2][groups][NACC][32]
+    const int lane = threadIdx.x % kWarp, grp = threadIdx.x / kWarp;
+    const int bt = blockIdx.x;
+    const int b0 = bt * tb;
+    const int i0 = blockIdx.y * kWarp;
+    const int i = i0 + lane;
+    const int K = table_rows(R);
+    const IO* __restrict__ x = static_cast<const IO*>(a.x);
+    const IO* __restrict__ gsrc = static_cast<const IO*>(EDGES ? a.gpostacts : a.gy);
+    const int row0 = grp * rpg;
+
+    for (int j = 0; j < rpg; ++j) {
+        const int row = row0 + j;
+        float v = 0.f;
+        if (b0 + row < a.batch && i < a.in_dim) v = ld_as_float(x + (size_t)(b0 + row) * a.in_dim + i);
+        x_s[row * 32 + lane] = v;
+        gx_s[row * 32 + lane] = 0.f;
+        if (BASE) {
+            float sg = sigmoid_f(v);
+            sl_s[row * 32 + lane] = v * sg;
+            dsl_s[row * 32 + lane] = sg * (1.f + v * (1.f - sg));
+        }
+    }
+    // each thread only ever touches its own column of its own group's rows: no barrier needed
+
+    for (int o = 0; o < a.out_dim; ++o) {
+        const float* t = a.table + (size_t)o * K * a.ipad + i;
+        EdgeFwd<R> e;
+        e.load(t, a.ipad);
+        e.load_bwd_extra(t, a.ipad);
+        float bw = 0.f;
+        if (BASE) bw = t[(size_t)t_bw(R) * a.ipad];
+        float acc[NACC];
+#pragma unroll
+        for (int k = 0; k < NACC; ++k) acc[k] = 0.f;
+
+        for (int j = 0; j < rpg; j += RU) {
+            float xv[RU], g[RU], sl[RU], dsl[RU];
+#pragma unroll
+            for (int u = 0; u < RU; ++u) {
+                const int row = row0 + j + u;
+                const int b = b0 + row;
+                xv[u] = x_s[row * 32 + lane];
+                sl[u] = BASE ? sl_s[row * 32 + lane] : 0.f;
+                dsl[u] = BASE ? dsl_s[row * 32 + lane] : 0.f;
+                g[u] = 0.f;
+                if (EDGES) {
+                    if (b < a.batch && i < a.in_dim)
+                        g[u] = ld_as_float(gsrc + ((size_t)b * a.out_dim + o) * a.in_dim + i);
+                } else {
+                    if (b < a.batch) g[u] = ld_as_float(gsrc + (size_t)b * a.out_dim + o);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < RU; ++u) {
+                const int row = row0 + j + u;
+                float gx = edge_backward<R, FAST, BASE, EDGES, NACC>(e, bw, xv[u], g[u], sl[u],
+                                                                     dsl[u], acc);
+                gx_s[row * 32 + lane] += gx;
+            }
+        }
+
+        // block-level reduction over the row groups, then this tile's partial
+        float* red = red_s + (size_t)(o & 1) * groups * NACC * 32;
+#pragma unroll
+        for (int k = 0; k < NACC; ++k) red[(grp * NACC + k) * 32 + lane] = acc[k];
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < NACC * 32; idx += blockDim.x) {
+            const int k = idx / 32, l = idx % 32;
+            float s = 0.f;
+            for (int gi = 0; gi < groups; ++gi) s += red[(gi * NACC + k) * 32 + l];
+            a.partials[(((size_t)bt * a.out_dim + o) * NACC + k) * a.ipad + i0 + l] = s;
+        }
+    }
+
+    if (a.gx) {
+        IO* __restrict__ gx = static_cast<IO*>(a.gx);
+        for (int j = 0; j < rpg; ++j) {
+            const int row = row0 + j;
+            if (b0 + row < a.batch && i < a.in_dim)
+                st_from_float(gx + (size_t)(b0 + row) * a.in_dim + i, gx_s[row * 32 + lane]);
+        }
+    }
+}
+
+BwdCfg choose_bwd_cfg(const QkDesc& d, bool base) {
+    const int nacc = acc_rows(d.reps, base);
+    const int grid_i = (d.in_dim + 31) / 32;
+    const size_t budget = 200 * 1024;
+    static const int cand[][2] = {{16, 32}, {16, 16}, {8, 32}, {8, 16}, {16, 8}, {8, 8}, {4, 8}, {2, 8}, {1, 8}};
+    BwdCfg best{};
+    long best_ctas = -1;
+    for (auto& c : cand) {
+        const int groups = c[0], rpg = c[1], tb = groups * rpg;
+        size_t smem = (size_t)tb * 32 * 4 * (base ? 4 : 2) + (size_t)2 * groups * nacc * 32 * 4;
+        if (smem > budget) continue;
+        const int grid_b = (d.batch + tb - 1) / tb;
+        const long ctas = (long)grid_b * grid_i;
+        BwdCfg cur{groups, rpg, tb, grid_b, grid_i, nacc, smem};
+        if (ctas >= 296) return cur;  // first (largest) tile that still fills the machine twice
+        if (ctas > best_ctas) {
+            best = cur;
+            best_ctas = ctas;
+        }
+    }
+    return best;
+}
+
+template <int R, bool FAST, typename IO, bool BASE, bool EDGES>
+static cudaError_t launch_bwd_t(const BwdArgs& a, cudaStream_t st) {
+    auto kern = backward_kernel<R, FAST, IO, BASE, EDGES, 2>;
+    cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           (int)a.cfg.smem);
+    if (err != cudaSuccess) return err;
+    dim3 grid(a.cfg.grid_b, a.cfg.grid_i);
+    kern<<<grid, a.cfg.groups * kWarp, a.cfg.smem, st>>>(a);
+    return cudaPeekAtLastError();
+}
+
+template <int R, bool FAST, typename IO>
+static cudaError_t launch_bwd_r(const BwdArgs& a, bool has_base, cudaStream_t st) {
+    if (a.gpostacts) return launch_bwd_t<R, FAST, IO, false, true>(a, st);
+    if (has_base) return launch_bwd_t<R, FAST, IO, true, false>(a, st);
+    return launch_bwd_t<R, FAST, IO, false, false>(a, st);
+}
+
+template <int R>
+static cudaError_t launch_bwd_d(const BwdArgs& a, bool fast, int io_dtype, bool has_base,
+                                cudaStream_t st) {
+    if (io_dtype == QK_BF16) {
+        return fast ? launch_bwd_r<R, true, __nv_bfloat16>(a, has_base, st)
+                    : launch_bwd_r<R, false, __nv_bfloat16>(a, has_base, st);
+    }
+    return fast ? launch_bwd_r<R, true, float>(a, has_base, st)
+                : launch_bwd_r<R, false, float>(a, has_base, st);
+}
+
+cudaError_t launch_backward(const BwdArgs& a, int reps, bool fast, int io_dtype, bool has_base,
+                            cudaStream_t st) {
+    switch (reps) {
+        case 1: return launch_bwd_d<1>(a, fast, io_dtype, has_base, st);
+        case 2: return launch_bwd_d<2>(a, fast, io_dtype, has_base, st);
+        case 3: return launch_bwd_d<3>(a, fast, io_dtype, has_base, st);
+        case 4: return launch_bwd_d<4>(a, fast, io_dtype, has_base, st);
+        case 5: return launch_bwd_d<5>(a, fast, io_dtype, has_base, st);
+        case 6: return launch_bwd_d<6>(a, fast, io_dtype, has_base, st);
+        case 7: return launch_bwd_d<7>(a, fast, io_dtype, has_base, st);
+        case 8: return launch_bwd_d<8>(a, fast, io_dtype, has_base, st);
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+}  // namespace qk

@@ -1,0 +1,197 @@
+// Shared definitions of the sm_100a QKANLayer kernels: the per-edge constant
+// table, the Bloch-vector circuit evaluation and its reverse sweep.
+//
+// Mathematics (pz_encoding; reference: src/qkan/solver/exact.py:90-134 with the
+// gates of src/qkan/torch_qc.py:76-121 and the readout of :261-277).
+// The reference evolves two complex amplitudes through H, then per repetition
+// Rz(theta[l,0]) Ry(theta[l,1]) Rz(enc_l), then Rz(theta[R,0]) Ry(theta[R,1]),
+// and reads |a|-|b| (fast) or |a|^2-|b|^2 (Born). Here the same state is the
+// real Bloch vector v = (vx,vy,vz):
+//   H|0>            -> v = (1,0,0)
+//   Rz(phi)         -> rotation of (vx,vy) by +phi
+//   Ry(phi)         -> (vx,vz) <- (vx cos + vz sin, vz cos - vx sin)
+//   Born readout    -> vz
+//   fast readout    -> vz * rsqrt(1 + sqrt(vx^2+vy^2))
+// Adjacent Rz gates are merged: Rz(enc_l) Rz(theta[l+1,0]) = Rz(pw_l x + c_l) with
+// c_l = pb_l + theta[l+1,0]; the leading Rz(theta[0,0]) Ry(theta[0,1]) acts on a
+// constant and is folded into the start vector.
+// Backward: with a the cotangent of v, the vector w = v x a transforms by the
+// same rotations as v, and the derivative with respect to a gate's angle is the
+// component of w along that gate's axis. One 3-vector is therefore swept back
+// through the gates (4 flops per gate) and no intermediate state is stored.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/qkan_b200.h"
+
+namespace qk {
+
+constexpr int kWarp = 32;
+constexpr int kMaxRepsTemplated = 8;
+
+// ---- per-edge constant table -------------------------------------------------
+// table[(o * K + k) * ipad + i], float32, ipad = in_dim rounded up to 32.
+__host__ __device__ constexpr int t_vx0() { return 0; }
+__host__ __device__ constexpr int t_vy0() { return 1; }
+__host__ __device__ constexpr int t_vz0() { return 2; }
+__host__ __device__ constexpr int t_pw(int l) { return 3 + 2 * l; }
+__host__ __device__ constexpr int t_c(int l) { return 4 + 2 * l; }
+__host__ __device__ constexpr int t_ca(int R, int l) { return 3 + 2 * R + 2 * (l - 1); }  // l >= 1
+__host__ __device__ constexpr int t_sa(int R, int l) { return 4 + 2 * R + 2 * (l - 1); }  // l >= 1
+__host__ __device__ constexpr int t_cf(int R) { return 4 * R + 1; }
+__host__ __device__ constexpr int t_sf(int R) { return 4 * R + 2; }
+__host__ __device__ constexpr int t_w(int R) { return 4 * R + 3; }    // postact_weights * mask
+__host__ __device__ constexpr int t_ca0(int R) { return 4 * R + 4; }  // cos/sin theta[0,1] (backward)
+__host__ __device__ constexpr int t_sa0(int R) { return 4 * R + 5; }
+__host__ __device__ constexpr int t_bw(int R) { return 4 * R + 6; }  // base_weight * mask
+__host__ __device__ constexpr int table_rows(int R) { return 4 * R + 7; }
+
+// accumulators of the backward, per edge, summed over the batch
+//   [0,R]      d/d theta[l,1]              (l = R is the final Ry)
+//   R+1+l      d/d c_l  = d/d theta[l+1,0] = d/d preacts_bias[l]
+//   2R+1+l     sum g_l * x = d/d preacts_weight[l]
+//   3R+1       d/d theta[0,0]
+//   3R+2       sum grad_y * postact  (-> d/d postact_weights)
+//   3R+3       sum grad_y * silu(x)  (-> d/d base_weight), only with the base term
+__host__ __device__ constexpr int a_ry(int l) { return l; }
+__host__ __device__ constexpr int a_c(int R, int l) { return R + 1 + l; }
+__host__ __device__ constexpr int a_pwx(int R, int l) { return 2 * R + 1 + l; }
+__host__ __device__ constexpr int a_t00(int R) { return 3 * R + 1; }
+__host__ __device__ constexpr int a_w(int R) { return 3 * R + 2; }
+__host__ __device__ constexpr int a_bw(int R) { return 3 * R + 3; }
+__host__ __device__ constexpr int acc_rows(int R, bool base) { return 3 * R + 3 + (base ? 1 : 0); }
+
+inline __host__ __device__ int round_up(int v, int m) { return (v + m - 1) / m * m; }
+inline __host__ __device__ size_t align256(size_t v) { return (v + 255) & ~size_t(255); }
+
+// ---- typed loads / stores ----------------------------------------------------
+template <typename T>
+__device__ __forceinline__ float ld_as_float(const T* p);
+template <>
+__device__ __forceinline__ float ld_as_float<float>(const float* p) {
+    return __ldg(p);
+}
+template <>
+__device__ __forceinline__ float ld_as_float<__nv_bfloat16>(const __nv_bfloat16* p) {
+    return __bfloat162float(__ldg(p));
+}
+template <typename T>
+__device__ __forceinline__ void st_from_float(T* p, float v);
+template <>
+__device__ __forceinline__ void st_from_float<float>(float* p, float v) {
+    *p = v;
+}
+template <>
+__device__ __forceinline__ void st_from_float<__nv_bfloat16>(__nv_bfloat16* p, float v) {
+    *p = __float2bfloat16_rn(v);
+}
+
+__device__ __forceinline__ float ld_param(const void* p, int dtype, size_t idx) {
+    return dtype == QK_BF16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(p)[idx])
+                            : static_cast<const float*>(p)[idx];
+}
+
+// ---- fast math ---------------------------------------------------------------
+// sin/cos of the data angle on the special-function unit. The angles are
+// pw*x + c with |c| <= ~2*pi and moderate |pw*x|; the unit's absolute error is
+// ~4e-7 there, well inside the 1e-5 normalised tolerance of the layer outputs.
+__device__ __forceinline__ void fast_sincos(float a, float& s, float& c) {
+#ifdef QK_PRECISE_TRIG
+    sincosf(a, &s, &c);
+#else
+    s = __sinf(a);
+    c = __cosf(a);
+#endif
+}
+__device__ __forceinline__ float fast_rsqrt(float a) {
+    float r;
+    asm("rsqrt.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(a));
+    return r;
+}
+__device__ __forceinline__ float fast_sqrt(float a) {
+    float r;
+    asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(a));
+    return r;
+}
+
+// ---- per-edge constants in registers -----------------------------------------
+template <int R>
+struct EdgeFwd {
+    float vx0, vy0, vz0;
+    float pw[R], c[R];
+    float ca[R], sa[R];  // index 0 unused in the forward
+    float cf, sf, w;
+
+    __device__ __forceinline__ void load(const float* __restrict__ t, int stride) {
+        vx0 = t[t_vx0() * stride];
+        vy0 = t[t_vy0() * stride];
+        vz0 = t[t_vz0() * stride];
+#pragma unroll
+        for (int l = 0; l < R; ++l) {
+            pw[l] = t[t_pw(l) * stride];
+            c[l] = t[t_c(l) * stride];
+        }
+#pragma unroll
+        for (int l = 1; l < R; ++l) {
+            ca[l] = t[t_ca(R, l) * stride];
+            sa[l] = t[t_sa(R, l) * stride];
+        }
+        cf = t[t_cf(R) * stride];
+        sf = t[t_sf(R) * stride];
+        w = t[t_w(R) * stride];
+    }
+    __device__ __forceinline__ void load_bwd_extra(const float* __restrict__ t, int stride) {
+        ca[0] = t[t_ca0(R) * stride];
+        sa[0] = t[t_sa0(R) * stride];
+    }
+};
+
+// Forward of one edge for one batch row: returns the readout p (before bias and weight).
+// When KEEP is true the data-gate sin/cos and the final Bloch vector are returned for the backward.
+template <int R, bool FAST, bool KEEP>
+__device__ __forceinline__ float edge_forward(const EdgeFwd<R>& e, float x, float* cs, float* sn,
+                                              float& vx, float& vy, float& vz, float& inv_rho,
+                                              float& r) {
+    vx = e.vx0;
+    vy = e.vy0;
+    vz = e.vz0;
+#pragma unroll
+    for (int l = 0; l < R; ++l) {
+        if (l > 0) {  // Ry(theta[l,1])
+            float nx = fmaf(vz, e.sa[l], vx * e.ca[l]);
+            float nz = fmaf(-vx, e.sa[l], vz * e.ca[l]);
+            vx = nx;
+            vz = nz;
+        }
+        float s, c;
+        fast_sincos(fmaf(e.pw[l], x, e.c[l]), s, c);  // merged Rz(pw_l x + pb_l + theta[l+1,0])
+        if (KEEP) {
+            cs[l] = c;
+            sn[l] = s;
+        }
+        float nx = fmaf(-vy, s, vx * c);
+        float ny = fmaf(vx, s, vy * c);
+        vx = nx;
+        vy = ny;
+    }
+    {  // final Ry(theta[R,1])
+        float nx = fmaf(vz, e.sf, vx * e.cf);
+        float nz = fmaf(-vx, e.sf, vz * e.cf);
+        vx = nx;
+        vz = nz;
+    }
+    if (!FAST) return vz;
+    float s2 = fmaf(vx, vx, vy * vy);
+    if (KEEP) {
+        inv_rho = fast_rsqrt(fmaxf(s2, 1e-30f));
+        r = fast_rsqrt(fmaf(s2, inv_rho, 1.0f));
+    } else {
+        r = fast_rsqrt(1.0f + fast_sqrt(s2));
+    }
+    return vz * r;
+}
+
+}  // namespace qk

@@ -1,0 +1,183 @@
+// Fused forward: y[b,o] = sum_i (p[b,o,i] + PB[o,i]) * W[o,i] + sum_i silu(x[b,i]) * BW[o,i]
+// with p the circuit readout of edge (o,i) on row b. Replaces the solver call,
+// the mask fold and the epilogue of QKANLayer._forward_train / _forward_eval
+// (reference: src/qkan/qkan.py:727-785; fused reference counterparts:
+// src/qkan/csrc/cute_kernels.cu:96-210 and src/qkan/qkan_epilogue.py:61-165).
+//
+// Mapping: a lane owns one input column i, a warp owns one output o at a time,
+// and both walk the CTA's batch rows. The edge's constants sit in registers,
+// the x tile is staged once in shared memory with coalesced loads, and the sum
+// over in_dim is a warp-shuffle transpose-reduction done once per 32 rows.
+#include "qk_kernels.cuh"
+
+namespace qk {
+
+// v[j] holds this lane's value for row j (j = 0..31). On return v[0] of lane L
+// is the sum over all lanes of their v[L]: 31 shuffles for 32 sums.
+__device__ __forceinline__ float transpose_reduce32(float (&v)[32], int lane) {
+#pragma unroll
+    for (int s = 16; s >= 1; s >>= 1) {
+        const bool up = (lane & s) != 0;
+#pragma unroll
+        for (int j = 0; j < s; ++j) {
+            float send = up ? v[j] : v[j + s];
+            float keep = up ? v[j + s] : v[j];
+            v[j] = keep + __shfl_xor_sync(0xffffffffu, send, s);
+        }
+    }
+    return v[0];
+}
+
+__device__ __forceinline__ float silu_f(float v) { return v / (1.f + expf(-v)); }
+
+template <int R, bool FAST, typename IO, bool BASE, bool EDGES>
+__global__ void __launch_bounds__(512) forward_kernel(FwdArgs a) {
+    extern __shared__ __align__(16) float smem[];
+    const int tb = a.cfg.tb, ot = a.cfg.ot, ich = a.cfg.ich;
+    const int ldy = tb + 1;
+    float* x_s = smem;                           // [tb][ich]
+    float* y_s = x_s + (size_t)tb * ich;         // [ot][tb+1]
+    float* b_s = y_s + (EDGES ? 0 : (size_t)ot * ldy);  // [tb][ich] silu(x), BASE only
+    const int b0 = blockIdx.x * tb;
+    const int o0 = blockIdx.y * ot;
+    const int ot_eff = min(ot, a.out_dim - o0);
+    const int warp = threadIdx.x / kWarp, lane = threadIdx.x % kWarp;
+    const int nwarps = blockDim.x / kWarp;
+    const int K = table_rows(R);
+    const IO* __restrict__ x = static_cast<const IO*>(a.x);
+
+    if (!EDGES)
+        for (int idx = threadIdx.x; idx < ot * ldy; idx += blockDim.x) y_s[idx] = 0.f;
+
+    for (int ic0 = 0; ic0 < a.ipad; ic0 += ich) {
+        const int w = min(ich, a.ipad - ic0);  // multiple of 32
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < tb * w; idx += blockDim.x) {
+            int r = idx / w, c = idx - r * w;
+            float v = 0.f;
+            if (b0 + r < a.batch && ic0 + c < a.in_dim)
+                v = ld_as_float(x + (size_t)(b0 + r) * a.in_dim + ic0 + c);
+            x_s[r * ich + c] = v;
+            if (BASE) b_s[r * ich + c] = silu_f(v);
+        }
+        __syncthreads();
+        const int nsub = w / kWarp;
+        for (int ol = warp; ol < ot_eff; ol += nwarps) {
+            const int o = o0 + ol;
+            for (int sub = 0; sub < nsub; ++sub) {
+                const int col = sub * kWarp + lane;
+                const int i = ic0 + col;
+                const float* t = a.table + (size_t)o * K * a.ipad + i;
+                EdgeFwd<R> e;
+                e.load(t, a.ipad);
+                float bw = 0.f;
+                if (BASE) bw = t[(size_t)t_bw(R) * a.ipad];
+                for (int rg = 0; rg < tb; rg += 32) {
+                    float v[32];
+#pragma unroll
+                    for (int r = 0; r < 32; ++r) {
+                        float xv = x_s[(rg + r) * ich + col];
+                        float vx, vy, vz, ir, rr;
+                        float p = edge_forward<R, FAST, false>(e, xv, nullptr, nullptr, vx, vy, vz,
+                                                               ir, rr);
+                        if (EDGES) {
+                            v[r] = p;
+                        } else {
+                            float val = p * e.w;
+                            if (BASE) val = fmaf(b_s[(rg + r) * ich + col], bw, val);
+                            v[r] = val;
+                        }
+                    }
+                    if (EDGES) {
+                        IO* out = static_cast<IO*>(a.postacts);
+                        if (i < a.in_dim) {
+#pragma unroll
+                            for (int r = 0; r < 32; ++r)
+                                if (b0 + rg + r < a.batch)
+                                    st_from_float(out + ((size_t)(b0 + rg + r) * a.out_dim + o) * a.in_dim + i,
+                                                  v[r]);
+                        }
+                    } else {
+                        float s = transpose_reduce32(v, lane);
+                        y_s[ol * ldy + rg + lane] += s;
+                    }
+                }
+            }
+        }
+    }
+    if (EDGES) return;
+    __syncthreads();
+    IO* __restrict__ y = static_cast<IO*>(a.y);
+    for (int idx = threadIdx.x; idx < tb * ot_eff; idx += blockDim.x) {
+        int r = idx / ot_eff, ol = idx - r * ot_eff;
+        if (b0 + r < a.batch)
+            st_from_float(y + (size_t)(b0 + r) * a.out_dim + o0 + ol,
+                          y_s[ol * ldy + r] + a.bias[o0 + ol]);
+    }
+}
+
+FwdCfg choose_fwd_cfg(const QkDesc& d, bool edges, bool base) {
+    FwdCfg c;
+    const int ipad = round_up(d.in_dim, 32);
+    c.threads = 512;
+    c.ich = ipad < 256 ? ipad : 256;
+    c.ot = d.out_dim < 256 ? d.out_dim : 256;
+    c.tb = 64;
+    // small problems: shrink the tile until the grid covers the machine twice
+    auto ctas = [&](int tb, int ot) {
+        return (long)((d.batch + tb - 1) / tb) * ((d.out_dim + ot - 1) / ot);
+    };
+    if (ctas(c.tb, c.ot) < 296) c.tb = 32;
+    while (ctas(c.tb, c.ot) < 296 && c.ot > 16) c.ot = (c.ot + 1) / 2;
+    c.grid_b = (d.batch + c.tb - 1) / c.tb;
+    c.grid_o = (d.out_dim + c.ot - 1) / c.ot;
+    // x tile + y tile + (with the base term) silu(x) tile
+    c.smem = (size_t)c.tb * c.ich * 4 * (base ? 2 : 1) + (edges ? 0 : (size_t)c.ot * (c.tb + 1) * 4);
+    return c;
+}
+
+template <int R, bool FAST, typename IO, bool BASE, bool EDGES>
+static cudaError_t launch_fwd_t(const FwdArgs& a, cudaStream_t st) {
+    auto kern = forward_kernel<R, FAST, IO, BASE, EDGES>;
+    cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           (int)a.cfg.smem);
+    if (err != cudaSuccess) return err;
+    dim3 grid(a.cfg.grid_b, a.cfg.grid_o);
+    kern<<<grid, a.cfg.threads, a.cfg.smem, st>>>(a);
+    return cudaPeekAtLastError();
+}
+
+template <int R, bool FAST, typename IO>
+static cudaError_t launch_fwd_r(const FwdArgs& a, bool has_base, cudaStream_t st) {
+    if (a.postacts) return launch_fwd_t<R, FAST, IO, false, true>(a, st);
+    if (has_base) return launch_fwd_t<R, FAST, IO, true, false>(a, st);
+    return launch_fwd_t<R, FAST, IO, false, false>(a, st);
+}
+
+template <int R>
+static cudaError_t launch_fwd_d(const FwdArgs& a, bool fast, int io_dtype, bool has_base,
+                                cudaStream_t st) {
+    if (io_dtype == QK_BF16) {
+        return fast ? launch_fwd_r<R, true, __nv_bfloat16>(a, has_base, st)
+                    : launch_fwd_r<R, false, __nv_bfloat16>(a, has_base, st);
+    }
+    return fast ? launch_fwd_r<R, true, float>(a, has_base, st)
+                : launch_fwd_r<R, false, float>(a, has_base, st);
+}
+
+cudaError_t launch_forward(const FwdArgs& a, int reps, bool fast, int io_dtype, bool has_base,
+                           cudaStream_t st) {
+    switch (reps) {
+        case 1: return launch_fwd_d<1>(a, fast, io_dtype, has_base, st);
+        case 2: return launch_fwd_d<2>(a, fast, io_dtype, has_base, st);
+        case 3: return launch_fwd_d<3>(a, fast, io_dtype, has_base, st);
+        case 4: return launch_fwd_d<4>(a, fast, io_dtype, has_base, st);
+        case 5: return launch_fwd_d<5>(a, fast, io_dtype, has_base, st);
+        case 6: return launch_fwd_d<6>(a, fast, io_dtype, has_base, st);
+        case 7: return launch_fwd_d<7>(a, fast, io_dtype, has_base, st);
+        case 8: return launch_fwd_d<8>(a, fast, io_dtype, has_base, st);
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+}  // namespace qk

@@ -1,0 +1,90 @@
+// Argument blocks and host-side launchers shared by the translation units.
+#pragma once
+
+#include "qk_common.cuh"
+
+namespace qk {
+
+struct PrepArgs {
+    int in_dim, out_dim, reps, ipad;
+    unsigned flags;
+    int param_dtype;
+    const float* theta;
+    const float* pw;
+    const float* pb;
+    const void* postw;  // nullptr => weight 1 (solver-contract mode)
+    const void* postb;
+    const void* basew;
+    const void* mask;
+    float* table;
+    float* bias;  // nullptr => not computed
+};
+
+struct FinishArgs {
+    int in_dim, out_dim, reps, ipad, nacc, ntiles, ncolsplit, has_base;
+    unsigned flags;
+    int param_dtype;
+    const float* partials;
+    const float* colsum;
+    const void* postw;
+    const void* postb;
+    const void* mask;
+    float* gtheta;
+    float* gpw;
+    float* gpb;
+    float* gpostw;
+    float* gpostb;
+    float* gbasew;
+};
+
+// Tile shape of the forward: a CTA owns `tb` batch rows and `ot` outputs and
+// walks the input dimension in chunks of `ich` (multiple of 32) columns.
+struct FwdCfg {
+    int tb, ot, ich, threads;
+    int grid_b, grid_o;
+    size_t smem;
+};
+
+// Tile shape of the backward: a CTA owns `groups * rpg` batch rows and 32 input
+// columns (one lane per column) and walks all outputs.
+struct BwdCfg {
+    int groups, rpg, tb;
+    int grid_b, grid_i;
+    int nacc;
+    size_t smem;
+};
+
+struct FwdArgs {
+    int batch, in_dim, out_dim, ipad;
+    FwdCfg cfg;
+    const void* x;
+    const float* table;
+    const float* bias;
+    void* y;         // (B,O), fused mode
+    void* postacts;  // (B,O,I), solver-contract mode (y unused)
+};
+
+struct BwdArgs {
+    int batch, in_dim, out_dim, ipad;
+    BwdCfg cfg;
+    const void* x;
+    const void* gy;         // (B,O) fused mode
+    const void* gpostacts;  // (B,O,I) solver-contract mode (gy unused)
+    const float* table;
+    void* gx;  // may be nullptr
+    float* partials;
+};
+
+FwdCfg choose_fwd_cfg(const QkDesc& d, bool edges, bool base);
+BwdCfg choose_bwd_cfg(const QkDesc& d, bool base);
+
+cudaError_t launch_prep(const PrepArgs& a, cudaStream_t st);
+cudaError_t launch_colsum(const void* gy, int io_dtype, int B, int O, int nsplit, float* part,
+                          cudaStream_t st);
+cudaError_t launch_finish(const FinishArgs& a, cudaStream_t st);
+cudaError_t launch_forward(const FwdArgs& a, int reps, bool fast, int io_dtype, bool has_base,
+                           cudaStream_t st);
+cudaError_t launch_backward(const BwdArgs& a, int reps, bool fast, int io_dtype, bool has_base,
+                            cudaStream_t st);
+
+}  // namespace qk

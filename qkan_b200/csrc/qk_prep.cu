@@ -1,0 +1,165 @@
+// Small set-up and finishing kernels around the two hot kernels:
+//   prep_table   : per-edge constant table (trig of theta, merged phases, folded mask)
+//   prep_bias    : bias[o] = sum_i postact_bias * postact_weights * mask
+//   colsum       : column sums of grad_y (needed by the postact_bias terms)
+//   finish_grads : fixed-order sum of the per-batch-tile partials into the
+//                  reference's parameter layouts
+#include "qk_kernels.cuh"
+
+namespace qk {
+
+__global__ void prep_table_kernel(PrepArgs a) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    const int o = blockIdx.y;
+    if (i >= a.ipad) return;
+    const int R = a.reps;
+    const int K = table_rows(R);
+    float* t = a.table + (size_t)o * K * a.ipad + i;
+    if (i >= a.in_dim) {
+        for (int k = 0; k < K; ++k) t[(size_t)k * a.ipad] = 0.f;
+        return;
+    }
+    const size_t e = (size_t)o * a.in_dim + i;
+    const float* th = a.theta + e * (R + 1) * 2;
+    const bool ptr = (a.flags & QK_PREACT_TRAINABLE) != 0;
+    float s00, c00, sa0, ca0;
+    sincosf(th[0], &s00, &c00);
+    sincosf(th[1], &sa0, &ca0);
+    // start vector: Ry(theta[0,1]) Rz(theta[0,0]) applied to (1,0,0)
+    t[(size_t)t_vx0() * a.ipad] = c00 * ca0;
+    t[(size_t)t_vy0() * a.ipad] = s00;
+    t[(size_t)t_vz0() * a.ipad] = -c00 * sa0;
+    t[(size_t)t_ca0(R) * a.ipad] = ca0;
+    t[(size_t)t_sa0(R) * a.ipad] = sa0;
+    for (int l = 0; l < R; ++l) {
+        float w = ptr ? a.pw[e * R + l] : 1.f;
+        float b = ptr ? a.pb[e * R + l] : 0.f;
+        t[(size_t)t_pw(l) * a.ipad] = w;
+        t[(size_t)t_c(l) * a.ipad] = b + th[2 * (l + 1)];
+        if (l >= 1) {
+            float s, c;
+            sincosf(th[2 * l + 1], &s, &c);
+            t[(size_t)t_ca(R, l) * a.ipad] = c;
+            t[(size_t)t_sa(R, l) * a.ipad] = s;
+        }
+    }
+    float sf, cf;
+    sincosf(th[2 * R + 1], &sf, &cf);
+    t[(size_t)t_cf(R) * a.ipad] = cf;
+    t[(size_t)t_sf(R) * a.ipad] = sf;
+    float m = a.mask ? ld_param(a.mask, a.param_dtype, e) : 1.f;
+    float w = a.postw ? ld_param(a.postw, a.param_dtype, e) * m : 1.f;
+    t[(size_t)t_w(R) * a.ipad] = w;
+    t[(size_t)t_bw(R) * a.ipad] = a.basew ? ld_param(a.basew, a.param_dtype, e) * m : 0.f;
+}
+
+// one warp per output: fixed lane-strided order + shuffle tree => deterministic
+__global__ void prep_bias_kernel(PrepArgs a) {
+    const int o = blockIdx.x * (blockDim.x / kWarp) + threadIdx.x / kWarp;
+    const int lane = threadIdx.x % kWarp;
+    if (o >= a.out_dim) return;
+    float s = 0.f;
+    if (a.postb && (a.flags & QK_USE_POSTACT_BIAS)) {
+        for (int i = lane; i < a.in_dim; i += kWarp) {
+            size_t e = (size_t)o * a.in_dim + i;
+            float m = a.mask ? ld_param(a.mask, a.param_dtype, e) : 1.f;
+            float w = a.postw ? ld_param(a.postw, a.param_dtype, e) * m : 1.f;
+            s = fmaf(ld_param(a.postb, a.param_dtype, e), w, s);
+        }
+    }
+#pragma unroll
+    for (int d = 16; d >= 1; d >>= 1) s += __shfl_xor_sync(0xffffffffu, s, d);
+    if (lane == 0) a.bias[o] = s;
+}
+
+// partial column sums: grid (ceil(O/32), nsplit); block (32, 8)
+template <typename IO>
+__global__ void colsum_kernel(const IO* __restrict__ gy, int B, int O, int nsplit,
+                              float* __restrict__ part) {
+    __shared__ float sm[8][kWarp];
+    const int o = blockIdx.x * kWarp + threadIdx.x;
+    const int split = blockIdx.y;
+    const int rows_per = (B + nsplit - 1) / nsplit;
+    const int r0 = split * rows_per;
+    const int r1 = min(B, r0 + rows_per);
+    float s = 0.f;
+    if (o < O)
+        for (int r = r0 + threadIdx.y; r < r1; r += 8) s += ld_as_float(gy + (size_t)r * O + o);
+    sm[threadIdx.y][threadIdx.x] = s;
+    __syncthreads();
+    if (threadIdx.y == 0 && o < O) {
+        float t = 0.f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) t += sm[k][threadIdx.x];
+        part[(size_t)split * O + o] = t;
+    }
+}
+
+__global__ void finish_grads_kernel(FinishArgs a) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    const int o = blockIdx.y;
+    if (i >= a.in_dim) return;
+    const int R = a.reps;
+    const int nacc = a.nacc;
+    const size_t e = (size_t)o * a.in_dim + i;
+    const bool ptr = (a.flags & QK_PREACT_TRAINABLE) != 0;
+    const bool use_pb = (a.flags & QK_USE_POSTACT_BIAS) != 0 && a.postb != nullptr;
+    const size_t tile_stride = (size_t)a.out_dim * nacc * a.ipad;
+    const float* p0 = a.partials + ((size_t)o * nacc) * a.ipad + i;
+    auto total = [&](int k) {
+        float s = 0.f;
+        const float* p = p0 + (size_t)k * a.ipad;
+        for (int t = 0; t < a.ntiles; ++t) s += p[(size_t)t * tile_stride];
+        return s;
+    };
+    if (a.gtheta) {
+        float* g = a.gtheta + e * (R + 1) * 2;
+        g[0] = total(a_t00(R));
+        for (int l = 0; l <= R; ++l) g[2 * l + 1] = total(a_ry(l));
+        for (int l = 0; l < R; ++l) g[2 * (l + 1)] = total(a_c(R, l));
+    }
+    if (a.gpb)
+        for (int l = 0; l < R; ++l) a.gpb[e * R + l] = ptr ? total(a_c(R, l)) : 0.f;
+    if (a.gpw)
+        for (int l = 0; l < R; ++l) a.gpw[e * R + l] = ptr ? total(a_pwx(R, l)) : 0.f;
+    if (a.gpostw || a.gpostb || a.gbasew) {
+        float cs = 0.f;
+        if (use_pb && a.colsum)
+            for (int s = 0; s < a.ncolsplit; ++s) cs += a.colsum[(size_t)s * a.out_dim + o];
+        float m = a.mask ? ld_param(a.mask, a.param_dtype, e) : 1.f;
+        if (a.gpostw) {
+            float pbv = use_pb ? ld_param(a.postb, a.param_dtype, e) : 0.f;
+            a.gpostw[e] = m * fmaf(pbv, cs, total(a_w(R)));
+        }
+        if (a.gpostb) {
+            float w = a.postw ? ld_param(a.postw, a.param_dtype, e) * m : 1.f;
+            a.gpostb[e] = use_pb ? w * cs : 0.f;
+        }
+        if (a.gbasew) a.gbasew[e] = a.has_base ? m * total(a_bw(R)) : 0.f;
+    }
+}
+
+cudaError_t launch_prep(const PrepArgs& a, cudaStream_t st) {
+    dim3 grid((a.ipad + 127) / 128, a.out_dim);
+    prep_table_kernel<<<grid, 128, 0, st>>>(a);
+    if (a.bias) prep_bias_kernel<<<(a.out_dim + 3) / 4, 128, 0, st>>>(a);
+    return cudaPeekAtLastError();
+}
+
+cudaError_t launch_colsum(const void* gy, int io_dtype, int B, int O, int nsplit, float* part,
+                          cudaStream_t st) {
+    dim3 grid((O + kWarp - 1) / kWarp, nsplit), block(kWarp, 8);
+    if (io_dtype == QK_BF16)
+        colsum_kernel<<<grid, block, 0, st>>>(static_cast<const __nv_bfloat16*>(gy), B, O, nsplit, part);
+    else
+        colsum_kernel<<<grid, block, 0, st>>>(static_cast<const float*>(gy), B, O, nsplit, part);
+    return cudaPeekAtLastError();
+}
+
+cudaError_t launch_finish(const FinishArgs& a, cudaStream_t st) {
+    dim3 grid((a.in_dim + 127) / 128, a.out_dim);
+    finish_grads_kernel<<<grid, 128, 0, st>>>(a);
+    return cudaPeekAtLastError();
+}
+
+}  // namespace qk

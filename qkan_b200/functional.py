@@ -1,0 +1,270 @@
+"""Tensor-level entry points over the C ABI: the fused layer op and the solver-contract op.
+
+``qkan_layer`` is the body of the reference's ``QKANLayer._forward_train`` after the
+optional batch-norm (``src/qkan/qkan.py:755-785``) as one differentiable op;
+``qkan_postacts`` is the reference's solver contract (``src/qkan/solver/_base.py:29-51``).
+torch is used for device memory, the current stream and autograd bookkeeping only.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import _abi
+
+_WORKSPACES: dict = {}
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
+    """Scratch owned by the caller side of the ABI: one growing buffer per (device, stream)."""
+    stream = torch.cuda.current_stream(device)
+    key = (device.index, stream.cuda_stream)
+    buf = _WORKSPACES.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=device)
+        _WORKSPACES[key] = buf
+    return buf
+
+
+def _io_dtype(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return _abi.QK_F32
+    if t.dtype == torch.bfloat16:
+        return _abi.QK_BF16
+    raise TypeError(f"qkan_b200 computes on float32 or bfloat16 activations, got {t.dtype}")
+
+
+def _require_cuda(t: torch.Tensor, name: str) -> None:
+    if not t.is_cuda:
+        raise RuntimeError(
+            f"qkan_b200: `{name}` is on {t.device}; the B200 kernels are the only compute path "
+            "(no CPU fallback)")
+
+
+def _f32c(t: torch.Tensor) -> torch.Tensor:
+    return t.detach().to(torch.float32).contiguous()
+
+
+def _flags(preact_trainable: bool, fast_measure: bool, use_postact_bias: bool) -> int:
+    return ((_abi.QK_PREACT_TRAINABLE if preact_trainable else 0)
+            | (_abi.QK_FAST_MEASURE if fast_measure else 0)
+            | (_abi.QK_USE_POSTACT_BIAS if use_postact_bias else 0))
+
+
+def _oi_params(postw, postb, basew, mask):
+    """Bring the (O,I) tensors to one dtype (float32 or bfloat16) and contiguity."""
+    tensors = [t for t in (postw, postb, basew, mask) if t is not None]
+    dt = torch.bfloat16 if all(t.dtype == torch.bfloat16 for t in tensors) else torch.float32
+    conv = lambda t: None if t is None else t.detach().to(dt).contiguous()  # noqa: E731
+    return conv(postw), conv(postb), conv(basew), conv(mask), (_abi.QK_BF16 if dt == torch.bfloat16 else _abi.QK_F32)
+
+
+def _make_desc(x, theta, flags, param_dtype) -> _abi.QkDesc:
+    B, I = x.shape
+    O, I2, R1, two = theta.shape
+    if I2 != I or two != 2:
+        raise ValueError(f"theta {tuple(theta.shape)} does not match x {tuple(x.shape)} "
+                         "(expected (out_dim, in_dim, reps+1, 2))")
+    return _abi.QkDesc(B, I, O, R1 - 1, _io_dtype(x), param_dtype, flags, 0)
+
+
+def layer_forward(x, theta, pw, pb, postw, postb=None, basew=None, mask=None, *,
+                  preact_trainable: bool, fast_measure: bool = True,
+                  use_postact_bias: bool = False) -> torch.Tensor:
+    """``y (B,O)`` of the fused layer; no autograd (see ``qkan_layer``)."""
+    lib = _abi.load()
+    _require_cuda(x, "x")
+    x = x.detach().contiguous()
+    theta, pw, pb = _f32c(theta), _f32c(pw), _f32c(pb)
+    postw, postb, basew, mask, pdt = _oi_params(postw, postb if use_postact_bias else None, basew, mask)
+    desc = _make_desc(x, theta, _flags(preact_trainable, fast_measure, use_postact_bias and postb is not None), pdt)
+    y = torch.empty((x.shape[0], theta.shape[0]), dtype=x.dtype, device=x.device)
+    with torch.cuda.device(x.device):
+        nbytes = lib.qk_forward_workspace_bytes(_abi.desc_pointer(desc))
+        ws = _workspace(x.device, nbytes)
+        rc = lib.qk_pz_forward(_abi.desc_pointer(desc), _ptr(x), _ptr(theta), _ptr(pw), _ptr(pb),
+                               _ptr(postw), _ptr(postb), _ptr(basew), _ptr(mask), _ptr(y),
+                               _ptr(ws), ws.numel(), torch.cuda.current_stream(x.device).cuda_stream)
+    _abi.check(rc, "qk_pz_forward")
+    return y
+
+
+def layer_backward(x, theta, pw, pb, postw, postb, basew, mask, gy, *, preact_trainable: bool,
+                   fast_measure: bool = True, use_postact_bias: bool = False,
+                   want=("x", "theta", "preacts_weight", "preacts_bias", "postact_weights",
+                         "postact_bias", "base_weight")) -> dict:
+    """Gradients of ``sum(y * gy)`` named as the reference's parameters; float32 except ``x``."""
+    lib = _abi.load()
+    _require_cuda(x, "x")
+    x = x.detach().contiguous()
+    gy = gy.detach().to(x.dtype).contiguous()
+    theta, pw, pb = _f32c(theta), _f32c(pw), _f32c(pb)
+    postw, postb, basew, mask, pdt = _oi_params(postw, postb if use_postact_bias else None, basew, mask)
+    desc = _make_desc(x, theta, _flags(preact_trainable, fast_measure, use_postact_bias and postb is not None), pdt)
+    O, I, R1, _ = theta.shape
+    dev = x.device
+    f32 = dict(dtype=torch.float32, device=dev)
+    out = {}
+    if "x" in want:
+        out["x"] = torch.empty_like(x)
+    if "theta" in want:
+        out["theta"] = torch.empty((O, I, R1, 2), **f32)
+    if "preacts_weight" in want:
+        out["preacts_weight"] = torch.empty((O, I, R1 - 1), **f32)
+    if "preacts_bias" in want:
+        out["preacts_bias"] = torch.empty((O, I, R1 - 1), **f32)
+    if "postact_weights" in want:
+        out["postact_weights"] = torch.empty((O, I), **f32)
+    if "postact_bias" in want:
+        out["postact_bias"] = torch.empty((O, I), **f32)
+    if "base_weight" in want:
+        out["base_weight"] = torch.empty((O, I), **f32)
+    with torch.cuda.device(dev):
+        nbytes = lib.qk_backward_workspace_bytes(_abi.desc_pointer(desc))
+        ws = _workspace(dev, nbytes)
+        rc = lib.qk_pz_backward(
+            _abi.desc_pointer(desc), _ptr(x), _ptr(theta), _ptr(pw), _ptr(pb), _ptr(postw),
+            _ptr(postb), _ptr(basew), _ptr(mask), _ptr(gy), _ptr(out.get("x")),
+            _ptr(out.get("theta")), _ptr(out.get("preacts_weight")), _ptr(out.get("preacts_bias")),
+            _ptr(out.get("postact_weights")), _ptr(out.get("postact_bias")),
+            _ptr(out.get("base_weight")), _ptr(ws), ws.numel(),
+            torch.cuda.current_stream(dev).cuda_stream)
+    _abi.check(rc, "qk_pz_backward")
+    return out
+
+
+def postacts_forward(x, theta, pw, pb, *, preact_trainable: bool, fast_measure: bool = True) -> torch.Tensor:
+    """Per-edge activations ``(B,O,I)`` (solver contract); no autograd."""
+    lib = _abi.load()
+    _require_cuda(x, "x")
+    x = x.detach().contiguous()
+    theta, pw, pb = _f32c(theta), _f32c(pw), _f32c(pb)
+    desc = _make_desc(x, theta, _flags(preact_trainable, fast_measure, False), _abi.QK_F32)
+    out = torch.empty((x.shape[0], theta.shape[0], x.shape[1]), dtype=x.dtype, device=x.device)
+    with torch.cuda.device(x.device):
+        nbytes = lib.qk_forward_workspace_bytes(_abi.desc_pointer(desc))
+        ws = _workspace(x.device, nbytes)
+        rc = lib.qk_pz_postacts_forward(_abi.desc_pointer(desc), _ptr(x), _ptr(theta), _ptr(pw),
+                                        _ptr(pb), _ptr(out), _ptr(ws), ws.numel(),
+                                        torch.cuda.current_stream(x.device).cuda_stream)
+    _abi.check(rc, "qk_pz_postacts_forward")
+    return out
+
+
+def postacts_backward(x, theta, pw, pb, gpostacts, *, preact_trainable: bool,
+                      fast_measure: bool = True,
+                      want=("x", "theta", "preacts_weight", "preacts_bias")) -> dict:
+    lib = _abi.load()
+    _require_cuda(x, "x")
+    x = x.detach().contiguous()
+    gpostacts = gpostacts.detach().to(x.dtype).contiguous()
+    theta, pw, pb = _f32c(theta), _f32c(pw), _f32c(pb)
+    desc = _make_desc(x, theta, _flags(preact_trainable, fast_measure, False), _abi.QK_F32)
+    O, I, R1, _ = theta.shape
+    f32 = dict(dtype=torch.float32, device=x.device)
+    out = {}
+    if "x" in want:
+        out["x"] = torch.empty_like(x)
+    if "theta" in want:
+        out["theta"] = torch.empty((O, I, R1, 2), **f32)
+    if "preacts_weight" in want:
+        out["preacts_weight"] = torch.empty((O, I, R1 - 1), **f32)
+    if "preacts_bias" in want:
+        out["preacts_bias"] = torch.empty((O, I, R1 - 1), **f32)
+    with torch.cuda.device(x.device):
+        nbytes = lib.qk_backward_workspace_bytes(_abi.desc_pointer(desc))
+        ws = _workspace(x.device, nbytes)
+        rc = lib.qk_pz_postacts_backward(
+            _abi.desc_pointer(desc), _ptr(x), _ptr(theta), _ptr(pw), _ptr(pb), _ptr(gpostacts),
+            _ptr(out.get("x")), _ptr(out.get("theta")), _ptr(out.get("preacts_weight")),
+            _ptr(out.get("preacts_bias")), _ptr(ws), ws.numel(),
+            torch.cuda.current_stream(x.device).cuda_stream)
+    _abi.check(rc, "qk_pz_postacts_backward")
+    return out
+
+
+class _LayerFunction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, theta, pw, pb, postw, postb, basew, mask, preact_trainable, fast_measure,
+                use_postact_bias):
+        ctx.save_for_backward(x, theta, pw, pb, postw, postb, basew, mask)
+        ctx.cfg = (preact_trainable, fast_measure, use_postact_bias)
+        return layer_forward(x, theta, pw, pb, postw, postb, basew, mask,
+                             preact_trainable=preact_trainable, fast_measure=fast_measure,
+                             use_postact_bias=use_postact_bias)
+
+    @staticmethod
+    def backward(ctx, gy):
+        x, theta, pw, pb, postw, postb, basew, mask = ctx.saved_tensors
+        preact_trainable, fast_measure, use_postact_bias = ctx.cfg
+        names = ("x", "theta", "preacts_weight", "preacts_bias", "postact_weights", "postact_bias",
+                 "base_weight")
+        need = ctx.needs_input_grad
+        want = tuple(n for k, n in enumerate(names) if need[k])
+        if not preact_trainable:
+            want = tuple(n for n in want if n not in ("preacts_weight", "preacts_bias"))
+        if postb is None or not use_postact_bias:
+            want = tuple(n for n in want if n != "postact_bias")
+        if basew is None:
+            want = tuple(n for n in want if n != "base_weight")
+        g = layer_backward(x, theta, pw, pb, postw, postb, basew, mask, gy,
+                           preact_trainable=preact_trainable, fast_measure=fast_measure,
+                           use_postact_bias=use_postact_bias, want=want)
+        srcs = (x, theta, pw, pb, postw, postb, basew)
+        outs = []
+        for k, n in enumerate(names):
+            t = g.get(n)
+            if t is not None and srcs[k] is not None:
+                t = t.to(srcs[k].dtype).reshape(srcs[k].shape)
+            outs.append(t)
+        return (*outs, None, None, None, None)
+
+
+def qkan_layer(x, theta, preacts_weight, preacts_bias, postact_weights, postact_bias=None,
+               base_weight=None, mask=None, *, preact_trainable: bool, fast_measure: bool = True,
+               use_postact_bias: bool = False) -> torch.Tensor:
+    """Differentiable fused QKAN layer ``(B,I) -> (B,O)`` on the CUDA kernels."""
+    return _LayerFunction.apply(x, theta, preacts_weight, preacts_bias, postact_weights,
+                                postact_bias, base_weight, mask, preact_trainable, fast_measure,
+                                use_postact_bias)
+
+
+class _PostactsFunction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, theta, pw, pb, preact_trainable, fast_measure):
+        ctx.save_for_backward(x, theta, pw, pb)
+        ctx.cfg = (preact_trainable, fast_measure)
+        return postacts_forward(x, theta, pw, pb, preact_trainable=preact_trainable,
+                                fast_measure=fast_measure)
+
+    @staticmethod
+    def backward(ctx, gpa):
+        x, theta, pw, pb = ctx.saved_tensors
+        preact_trainable, fast_measure = ctx.cfg
+        names = ("x", "theta", "preacts_weight", "preacts_bias")
+        need = ctx.needs_input_grad
+        want = tuple(n for k, n in enumerate(names) if need[k])
+        if not preact_trainable:
+            want = tuple(n for n in want if n not in ("preacts_weight", "preacts_bias"))
+        g = postacts_backward(x, theta, pw, pb, gpa, preact_trainable=preact_trainable,
+                              fast_measure=fast_measure, want=want)
+        srcs = (x, theta, pw, pb)
+        outs = []
+        for k, n in enumerate(names):
+            t = g.get(n)
+            if t is not None:
+                t = t.to(srcs[k].dtype).reshape(srcs[k].shape)
+            outs.append(t)
+        return (*outs, None, None)
+
+
+def qkan_postacts(x, theta, preacts_weight, preacts_bias, *, preact_trainable: bool,
+                  fast_measure: bool = True) -> torch.Tensor:
+    """Differentiable per-edge activations ``(B,O,I)`` — the reference solver contract."""
+    return _PostactsFunction.apply(x, theta, preacts_weight, preacts_bias, preact_trainable,
+                                   fast_measure)

@@ -1,0 +1,125 @@
+"""Parity of the CUDA path (through the C ABI) with the CPU oracle and the golden fixtures."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle
+from tests.util import (GRAD_NAMES, TOL_BF16, TOL_F32, case_inputs, golden_layer_cases, nerr,
+                        random_problem)
+
+pytestmark = pytest.mark.gpu
+
+
+def _dev(a, dtype=torch.float32):
+    return None if a is None else torch.as_tensor(np.asarray(a), dtype=dtype, device="cuda")
+
+
+def _run_cuda(p, cfg, io_dtype=torch.float32, param_dtype=torch.float32):
+    from qkan_b200 import functional as F
+
+    x = _dev(p["x"], io_dtype)
+    gy = _dev(p["gy"], io_dtype)
+    th, pw, pb = _dev(p["theta"]), _dev(p["pw"]), _dev(p["pb"])
+    postw, postb, basew, mask = (_dev(p[k], param_dtype) for k in ("postw", "postb", "basew", "mask"))
+    y = F.layer_forward(x, th, pw, pb, postw, postb, basew, mask, **cfg)
+    g = F.layer_backward(x, th, pw, pb, postw, postb, basew, mask, gy, **cfg)
+    torch.cuda.synchronize()
+    return y.float().cpu().numpy(), {k: v.float().cpu().numpy() for k, v in g.items()}
+
+
+def _run_oracle(p, cfg):
+    args = [p[k] for k in ("x", "theta", "pw", "pb", "postw", "postb", "basew", "mask")]
+    y = oracle.forward(*args, **cfg)
+    g = oracle.backward(*args, p["gy"], **cfg)
+    return y, g
+
+
+def _check(y, g, y_ref, g_ref, tol, label):
+    assert nerr(y, y_ref) <= tol, f"{label}: y err {nerr(y, y_ref):.3e}"
+    for k in GRAD_NAMES:
+        assert nerr(g[k], g_ref[k]) <= tol, f"{label}: grad {k} err {nerr(g[k], g_ref[k]):.3e}"
+
+
+@pytest.mark.parametrize("case", golden_layer_cases(), ids=lambda c: c["name"])
+def test_golden_cases_fp32(case):
+    """CUDA fp32 vs the reference's own float64 outputs stored in tests/golden."""
+    p = case_inputs(case)
+    y, g = _run_cuda(p, case["cfg"])
+    g_ref = {k: case["g_" + k] for k in GRAD_NAMES}
+    _check(y, g, case["y"], g_ref, TOL_F32, case["name"])
+
+
+@pytest.mark.parametrize("B,I,O,R", [(1, 1, 1, 1), (33, 7, 5, 2), (100, 40, 33, 3), (257, 64, 64, 3),
+                                     (64, 300, 9, 4), (50, 31, 70, 8), (1000, 1, 1, 3),
+                                     (513, 96, 17, 5), (70, 33, 300, 6), (40, 20, 10, 7)])
+@pytest.mark.parametrize("fast", [True, False])
+def test_oracle_parity_fp32(B, I, O, R, fast):
+    p = random_problem(B * 7 + I + R, B, I, O, R, use_pb=True, base=(R % 2 == 0), masked=(R % 3 == 0))
+    cfg = dict(preact_trainable=(O % 2 == 1) or R == 3, fast_measure=fast, use_postact_bias=True)
+    y, g = _run_cuda(p, cfg)
+    y_ref, g_ref = _run_oracle(p, cfg)
+    _check(y, g, y_ref, g_ref, TOL_F32, f"B{B} I{I} O{O} R{R}")
+
+
+@pytest.mark.parametrize("B,I,O,R", [(64, 64, 48, 1), (129, 96, 64, 2), (200, 128, 40, 4), (96, 70, 33, 8)])
+def test_oracle_parity_bf16_io(B, I, O, R):
+    """bf16 x / y / grad_y / grad_x and (O,I) tensors, fp32 theta and accumulation (tolerance 2e-2).
+
+    The oracle consumes the bf16-rounded inputs, as the parity protocol prescribes.
+    """
+    p = random_problem(B + I, B, I, O, R, use_pb=False, x_scale=3.0)
+    for k in ("x", "gy", "postw"):
+        p[k] = torch.as_tensor(p[k]).to(torch.bfloat16).float().numpy()
+    cfg = dict(preact_trainable=True, fast_measure=True, use_postact_bias=False)
+    y, g = _run_cuda(p, cfg, io_dtype=torch.bfloat16, param_dtype=torch.bfloat16)
+    y_ref, g_ref = _run_oracle(p, cfg)
+    _check(y, g, y_ref, g_ref, TOL_BF16, f"bf16 B{B} I{I} O{O} R{R}")
+
+
+def test_postacts_contract_matches_golden():
+    """Solver contract: (B,O,I) activations and their backward from a (B,O,I) cotangent."""
+    from qkan_b200 import functional as F
+
+    for case in golden_layer_cases():
+        p = case_inputs(case)
+        cfg = dict(preact_trainable=case["cfg"]["preact_trainable"], fast_measure=case["cfg"]["fast_measure"])
+        x, th, pw, pb = (_dev(p[k]) for k in ("x", "theta", "pw", "pb"))
+        pa = F.postacts_forward(x, th, pw, pb, **cfg)
+        assert nerr(pa.cpu().numpy(), case["postacts"]) <= TOL_F32, case["name"]
+        rng = np.random.default_rng(5)
+        gpa = rng.standard_normal(case["postacts"].shape).astype(np.float32)
+        g = F.postacts_backward(x, th, pw, pb, _dev(gpa), **cfg)
+        ref = oracle.backward(p["x"], p["theta"], p["pw"], p["pb"], p["postw"], None, None, None,
+                              np.zeros_like(p["gy"]), gpostacts=gpa, use_postact_bias=False, **cfg)
+        for k in ("x", "theta", "preacts_weight", "preacts_bias"):
+            assert nerr(g[k].cpu().numpy(), ref[k]) <= TOL_F32, (case["name"], k)
+
+
+def test_backward_is_bitwise_reproducible():
+    p = random_problem(3, 300, 70, 50, 3)
+    cfg = dict(preact_trainable=True, fast_measure=True, use_postact_bias=True)
+    _, g1 = _run_cuda(p, cfg)
+    _, g2 = _run_cuda(p, cfg)
+    for k in GRAD_NAMES:
+        assert np.array_equal(g1[k], g2[k]), k
+
+
+def test_empty_batch_and_bad_arguments():
+    from qkan_b200 import functional as F
+
+    p = random_problem(1, 4, 3, 2, 2)
+    cfg = dict(preact_trainable=True, fast_measure=True, use_postact_bias=False)
+    th, pw, pb, postw = (_dev(p[k]) for k in ("theta", "pw", "pb", "postw"))
+    x0 = torch.empty((0, 3), device="cuda")
+    y0 = F.layer_forward(x0, th, pw, pb, postw, **cfg)
+    assert y0.shape == (0, 2)
+    g0 = F.layer_backward(x0, th, pw, pb, postw, None, None, None, torch.empty((0, 2), device="cuda"), **cfg)
+    assert float(g0["theta"].abs().max()) == 0.0
+    with pytest.raises(ValueError):
+        F.layer_forward(torch.zeros((4, 5), device="cuda"), th, pw, pb, postw, **cfg)
+    with pytest.raises(NotImplementedError):
+        th9 = torch.zeros((2, 3, 10, 2), device="cuda")
+        F.layer_forward(_dev(p["x"]), th9, torch.zeros((2, 3, 9), device="cuda"),
+                        torch.zeros((2, 3, 9), device="cuda"), postw, **cfg)
+    with pytest.raises(RuntimeError):
+        F.layer_forward(torch.zeros((4, 3)), th, pw, pb, postw, **cfg)
