@@ -49,11 +49,27 @@ def is_stale() -> bool:
     return any(os.path.getmtime(p) > t for p in _deps())
 
 
-def _compile(src: str, extra) -> str:
-    obj = os.path.join(OBJ, os.path.basename(src)[:-3] + ".o")
-    cmd = [_nvcc(), *NVCC_FLAGS, *extra, "-c", src, "-o", obj]
+REPS_COMPILED = range(1, 9)  # the per-repetition template instantiations (csrc/*_inst.cu)
+
+
+def _jobs():
+    """(source, object stem, extra defines): *_inst.cu units are compiled once per repetition count."""
+    jobs = []
+    for src in _sources():
+        stem = os.path.basename(src)[:-3]
+        if stem.endswith("_inst"):
+            jobs += [(src, f"{stem}_r{r}", [f"-DQK_INST_R={r}"]) for r in REPS_COMPILED]
+        else:
+            jobs.append((src, stem, []))
+    return jobs
+
+
+def _compile(job, extra) -> str:
+    src, stem, defs = job
+    obj = os.path.join(OBJ, stem + ".o")
+    cmd = [_nvcc(), *NVCC_FLAGS, *defs, *extra, "-c", src, "-o", obj]
     res = subprocess.run(cmd, capture_output=True, text=True)
-    log = os.path.join(OBJ, os.path.basename(src)[:-3] + ".ptxas.log")
+    log = os.path.join(OBJ, stem + ".ptxas.log")
     with open(log, "w") as fh:
         fh.write(" ".join(cmd) + "\n" + res.stdout + res.stderr)
     if res.returncode != 0:
@@ -67,7 +83,7 @@ def build(force: bool = False, extra_flags=()) -> str:
         return LIB
     os.makedirs(OBJ, exist_ok=True)
     with cf.ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 1)) as pool:
-        objs = list(pool.map(lambda s: _compile(s, list(extra_flags)), _sources()))
+        objs = list(pool.map(lambda j: _compile(j, list(extra_flags)), _jobs()))
     res = subprocess.run([_nvcc(), "-shared", "-o", LIB, *objs, "-gencode",
                           "arch=compute_100a,code=sm_100a"], capture_output=True, text=True)
     if res.returncode != 0:

@@ -14,6 +14,7 @@
 // the groups' accumulators are summed through shared memory (block-level
 // reduction) and written as this batch tile's partial; finish_grads then sums
 // the tiles in a fixed order (cross-CTA reduction, bitwise reproducible).
+#pragma once
 #include "qk_kernels.cuh"
 
 namespace qk {
@@ -72,16 +73,17 @@ __device__ __forceinline__ float edge_backward(const EdgeFwd<R>& e, float bw, fl
     return gx;
 }
 
+constexpr int kGyChunk = 8;  // outputs whose grad_y columns are staged together
+
 template <int R, bool FAST, typename IO, bool BASE, bool EDGES, int RU>
 __global__ void __launch_bounds__(512) backward_kernel(BwdArgs a) {
     constexpr int NACC = acc_rows(R, BASE);
+    constexpr int ROW = BASE ? 128 : 64;  // floats per tile row: x | grad_x [| silu | silu']
     extern __shared__ __align__(16) float smem[];
     const int groups = a.cfg.groups, rpg = a.cfg.rpg, tb = a.cfg.tb;
-    float* x_s = smem;                     // [tb][32]
-    float* gx_s = x_s + (size_t)tb * 32;   // [tb][32]
-    float* sl_s = gx_s + (size_t)tb * 32;  // [tb][32] silu(x)        (BASE)
-    float* dsl_s = sl_s + (BASE ? (size_t)tb * 32 : 0);  // [tb][32] silu'(x) (BASE)
-    float* red_s = dsl_s + (BASE ? (size_t)tb * 32 : 0);  // [2][groups][NACC][32]
+    float* xg_s = smem;                                  // [tb][ROW]
+    float* gy_s = xg_s + (size_t)tb * ROW;               // [kGyChunk][tb]   (fused mode)
+    float* red_s = gy_s + (EDGES ? 0 : (size_t)kGyChunk * tb);  // [2][groups][NACC][32]
     const int lane = threadIdx.x % kWarp, grp = threadIdx.x / kWarp;
     const int bt = blockIdx.x;
     const int b0 = bt * tb;
@@ -91,68 +93,98 @@ __global__ void __launch_bounds__(512) backward_kernel(BwdArgs a) {
     const IO* __restrict__ x = static_cast<const IO*>(a.x);
     const IO* __restrict__ gsrc = static_cast<const IO*>(EDGES ? a.gpostacts : a.gy);
     const int row0 = grp * rpg;
+    float* const my = xg_s + (size_t)row0 * ROW + lane;  // this thread's column of its group's rows
 
     for (int j = 0; j < rpg; ++j) {
         const int row = row0 + j;
         float v = 0.f;
         if (b0 + row < a.batch && i < a.in_dim) v = ld_as_float(x + (size_t)(b0 + row) * a.in_dim + i);
-        x_s[row * 32 + lane] = v;
-        gx_s[row * 32 + lane] = 0.f;
+        my[j * ROW] = v;
+        my[j * ROW + 32] = 0.f;
         if (BASE) {
             float sg = sigmoid_f(v);
-            sl_s[row * 32 + lane] = v * sg;
-            dsl_s[row * 32 + lane] = sg * (1.f + v * (1.f - sg));
+            my[j * ROW + 64] = v * sg;
+            my[j * ROW + 96] = sg * (1.f + v * (1.f - sg));
         }
     }
-    // each thread only ever touches its own column of its own group's rows: no barrier needed
+    // a thread only ever touches its own column of its own group's rows: no barrier needed for xg_s
 
-    for (int o = 0; o < a.out_dim; ++o) {
-        const float* t = a.table + (size_t)o * K * a.ipad + i;
-        EdgeFwd<R> e;
-        e.load(t, a.ipad);
-        e.load_bwd_extra(t, a.ipad);
-        float bw = 0.f;
-        if (BASE) bw = t[(size_t)t_bw(R) * a.ipad];
-        float acc[NACC];
+    for (int oc = 0; oc < a.out_dim; oc += kGyChunk) {
+        const int nch = min(kGyChunk, a.out_dim - oc);
+        if (!EDGES) {
+            // stage grad_y[b0 .. b0+tb, oc .. oc+nch) transposed; rows past the batch read as 0
+            for (int idx = threadIdx.x; idx < tb * kGyChunk; idx += blockDim.x) {
+                const int r = idx / kGyChunk, c = idx % kGyChunk;
+                float v = 0.f;
+                if (b0 + r < a.batch && c < nch) v = ld_as_float(gsrc + (size_t)(b0 + r) * a.out_dim + oc + c);
+                gy_s[c * tb + r] = v;
+            }
+            __syncthreads();
+        }
+        for (int ol = 0; ol < nch; ++ol) {
+            const int o = oc + ol;
+            const float* t = a.table + (size_t)o * K * a.ipad + i;
+            EdgeFwd<R> e;
+            e.load(t, a.ipad);
+            e.load_bwd_extra(t, a.ipad);
+            float bw = 0.f;
+            if (BASE) bw = t[(size_t)t_bw(R) * a.ipad];
+            float acc[NACC];
 #pragma unroll
-        for (int k = 0; k < NACC; ++k) acc[k] = 0.f;
+            for (int k = 0; k < NACC; ++k) acc[k] = 0.f;
 
-        for (int j = 0; j < rpg; j += RU) {
-            float xv[RU], g[RU], sl[RU], dsl[RU];
+            const float* gyp = gy_s + ol * tb + row0;
+            float* p = my;
+#pragma unroll 1
+            for (int j = 0; j < rpg; j += RU, p += RU * ROW) {
+                float xv[RU], g[RU], sl[RU], dsl[RU];
 #pragma unroll
-            for (int u = 0; u < RU; ++u) {
-                const int row = row0 + j + u;
-                const int b = b0 + row;
-                xv[u] = x_s[row * 32 + lane];
-                sl[u] = BASE ? sl_s[row * 32 + lane] : 0.f;
-                dsl[u] = BASE ? dsl_s[row * 32 + lane] : 0.f;
-                g[u] = 0.f;
-                if (EDGES) {
-                    if (b < a.batch && i < a.in_dim)
-                        g[u] = ld_as_float(gsrc + ((size_t)b * a.out_dim + o) * a.in_dim + i);
-                } else {
-                    if (b < a.batch) g[u] = ld_as_float(gsrc + (size_t)b * a.out_dim + o);
+                for (int u = 0; u < RU; ++u) {
+                    xv[u] = p[u * ROW];
+                    sl[u] = BASE ? p[u * ROW + 64] : 0.f;
+                    dsl[u] = BASE ? p[u * ROW + 96] : 0.f;
+                    if (EDGES) {
+                        const int b = b0 + row0 + j + u;
+                        g[u] = 0.f;
+                        if (b < a.batch && i < a.in_dim)
+                            g[u] = ld_as_float(gsrc + ((size_t)b * a.out_dim + o) * a.in_dim + i);
+                    } else if (RU != 2 && RU != 4) {
+                        g[u] = gyp[j + u];
+                    }
+                }
+                // tb, row0 and j are multiples of RU, so the staged grad_y values of these rows
+                // are one aligned vector (same address in every lane: a broadcast load)
+                if (!EDGES && RU == 2) {
+                    const float2 gv = *reinterpret_cast<const float2*>(gyp + j);
+                    g[0] = gv.x;
+                    g[RU - 1] = gv.y;
+                }
+                if (!EDGES && RU == 4) {
+                    const float4 gv = *reinterpret_cast<const float4*>(gyp + j);
+                    g[0] = gv.x;
+                    g[1 % RU] = gv.y;
+                    g[2 % RU] = gv.z;
+                    g[3 % RU] = gv.w;
+                }
+#pragma unroll
+                for (int u = 0; u < RU; ++u) {
+                    float gx = edge_backward<R, FAST, BASE, EDGES, NACC>(e, bw, xv[u], g[u], sl[u],
+                                                                         dsl[u], acc);
+                    p[u * ROW + 32] += gx;
                 }
             }
-#pragma unroll
-            for (int u = 0; u < RU; ++u) {
-                const int row = row0 + j + u;
-                float gx = edge_backward<R, FAST, BASE, EDGES, NACC>(e, bw, xv[u], g[u], sl[u],
-                                                                     dsl[u], acc);
-                gx_s[row * 32 + lane] += gx;
-            }
-        }
 
-        // block-level reduction over the row groups, then this tile's partial
-        float* red = red_s + (size_t)(o & 1) * groups * NACC * 32;
+            // block-level reduction over the row groups, then this tile's partial
+            float* red = red_s + (size_t)(o & 1) * groups * NACC * 32;
 #pragma unroll
-        for (int k = 0; k < NACC; ++k) red[(grp * NACC + k) * 32 + lane] = acc[k];
-        __syncthreads();
-        for (int idx = threadIdx.x; idx < NACC * 32; idx += blockDim.x) {
-            const int k = idx / 32, l = idx % 32;
-            float s = 0.f;
-            for (int gi = 0; gi < groups; ++gi) s += red[(gi * NACC + k) * 32 + l];
-            a.partials[(((size_t)bt * a.out_dim + o) * NACC + k) * a.ipad + i0 + l] = s;
+            for (int k = 0; k < NACC; ++k) red[(grp * NACC + k) * 32 + lane] = acc[k];
+            __syncthreads();
+            for (int idx = threadIdx.x; idx < NACC * 32; idx += blockDim.x) {
+                const int k = idx / 32, l = idx % 32;
+                float s = 0.f;
+                for (int gi = 0; gi < groups; ++gi) s += red[(gi * NACC + k) * 32 + l];
+                a.partials[(((size_t)bt * a.out_dim + o) * NACC + k) * a.ipad + i0 + l] = s;
+            }
         }
     }
 
@@ -161,37 +193,15 @@ __global__ void __launch_bounds__(512) backward_kernel(BwdArgs a) {
         for (int j = 0; j < rpg; ++j) {
             const int row = row0 + j;
             if (b0 + row < a.batch && i < a.in_dim)
-                st_from_float(gx + (size_t)(b0 + row) * a.in_dim + i, gx_s[row * 32 + lane]);
+                st_from_float(gx + (size_t)(b0 + row) * a.in_dim + i, my[j * ROW + 32]);
         }
     }
-}
-
-BwdCfg choose_bwd_cfg(const QkDesc& d, bool base) {
-    const int nacc = acc_rows(d.reps, base);
-    const int grid_i = (d.in_dim + 31) / 32;
-    const size_t budget = 200 * 1024;
-    static const int cand[][2] = {{16, 32}, {16, 16}, {8, 32}, {8, 16}, {16, 8}, {8, 8}, {4, 8}, {2, 8}, {1, 8}};
-    BwdCfg best{};
-    long best_ctas = -1;
-    for (auto& c : cand) {
-        const int groups = c[0], rpg = c[1], tb = groups * rpg;
-        size_t smem = (size_t)tb * 32 * 4 * (base ? 4 : 2) + (size_t)2 * groups * nacc * 32 * 4;
-        if (smem > budget) continue;
-        const int grid_b = (d.batch + tb - 1) / tb;
-        const long ctas = (long)grid_b * grid_i;
-        BwdCfg cur{groups, rpg, tb, grid_b, grid_i, nacc, smem};
-        if (ctas >= 296) return cur;  // first (largest) tile that still fills the machine twice
-        if (ctas > best_ctas) {
-            best = cur;
-            best_ctas = ctas;
-        }
-    }
-    return best;
 }
 
 template <int R, bool FAST, typename IO, bool BASE, bool EDGES>
 static cudaError_t launch_bwd_t(const BwdArgs& a, cudaStream_t st) {
-    auto kern = backward_kernel<R, FAST, IO, BASE, EDGES, 2>;
+    auto kern = a.cfg.ru == 4 ? backward_kernel<R, FAST, IO, BASE, EDGES, 4>
+                              : backward_kernel<R, FAST, IO, BASE, EDGES, 2>;
     cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            (int)a.cfg.smem);
     if (err != cudaSuccess) return err;
@@ -208,7 +218,7 @@ static cudaError_t launch_bwd_r(const BwdArgs& a, bool has_base, cudaStream_t st
 }
 
 template <int R>
-static cudaError_t launch_bwd_d(const BwdArgs& a, bool fast, int io_dtype, bool has_base,
+cudaError_t launch_bwd_d(const BwdArgs& a, bool fast, int io_dtype, bool has_base,
                                 cudaStream_t st) {
     if (io_dtype == QK_BF16) {
         return fast ? launch_bwd_r<R, true, __nv_bfloat16>(a, has_base, st)
@@ -216,21 +226,6 @@ static cudaError_t launch_bwd_d(const BwdArgs& a, bool fast, int io_dtype, bool 
     }
     return fast ? launch_bwd_r<R, true, float>(a, has_base, st)
                 : launch_bwd_r<R, false, float>(a, has_base, st);
-}
-
-cudaError_t launch_backward(const BwdArgs& a, int reps, bool fast, int io_dtype, bool has_base,
-                            cudaStream_t st) {
-    switch (reps) {
-        case 1: return launch_bwd_d<1>(a, fast, io_dtype, has_base, st);
-        case 2: return launch_bwd_d<2>(a, fast, io_dtype, has_base, st);
-        case 3: return launch_bwd_d<3>(a, fast, io_dtype, has_base, st);
-        case 4: return launch_bwd_d<4>(a, fast, io_dtype, has_base, st);
-        case 5: return launch_bwd_d<5>(a, fast, io_dtype, has_base, st);
-        case 6: return launch_bwd_d<6>(a, fast, io_dtype, has_base, st);
-        case 7: return launch_bwd_d<7>(a, fast, io_dtype, has_base, st);
-        case 8: return launch_bwd_d<8>(a, fast, io_dtype, has_base, st);
-        default: return cudaErrorInvalidValue;
-    }
 }
 
 }  // namespace qk

@@ -102,8 +102,8 @@ __device__ __forceinline__ void fast_sincos(float a, float& s, float& c) {
 #ifdef QK_PRECISE_TRIG
     sincosf(a, &s, &c);
 #else
-    s = __sinf(a);
-    c = __cosf(a);
+    asm("sin.approx.ftz.f32 %0, %1;" : "=f"(s) : "f"(a));
+    asm("cos.approx.ftz.f32 %0, %1;" : "=f"(c) : "f"(a));
 #endif
 }
 __device__ __forceinline__ float fast_rsqrt(float a) {

@@ -8,6 +8,7 @@
 // and both walk the CTA's batch rows. The edge's constants sit in registers,
 // the x tile is staged once in shared memory with coalesced loads, and the sum
 // over in_dim is a warp-shuffle transpose-reduction done once per 32 rows.
+#pragma once
 #include "qk_kernels.cuh"
 
 namespace qk {
@@ -116,26 +117,6 @@ __global__ void __launch_bounds__(512) forward_kernel(FwdArgs a) {
     }
 }
 
-FwdCfg choose_fwd_cfg(const QkDesc& d, bool edges, bool base) {
-    FwdCfg c;
-    const int ipad = round_up(d.in_dim, 32);
-    c.threads = 512;
-    c.ich = ipad < 256 ? ipad : 256;
-    c.ot = d.out_dim < 256 ? d.out_dim : 256;
-    c.tb = 64;
-    // small problems: shrink the tile until the grid covers the machine twice
-    auto ctas = [&](int tb, int ot) {
-        return (long)((d.batch + tb - 1) / tb) * ((d.out_dim + ot - 1) / ot);
-    };
-    if (ctas(c.tb, c.ot) < 296) c.tb = 32;
-    while (ctas(c.tb, c.ot) < 296 && c.ot > 16) c.ot = (c.ot + 1) / 2;
-    c.grid_b = (d.batch + c.tb - 1) / c.tb;
-    c.grid_o = (d.out_dim + c.ot - 1) / c.ot;
-    // x tile + y tile + (with the base term) silu(x) tile
-    c.smem = (size_t)c.tb * c.ich * 4 * (base ? 2 : 1) + (edges ? 0 : (size_t)c.ot * (c.tb + 1) * 4);
-    return c;
-}
-
 template <int R, bool FAST, typename IO, bool BASE, bool EDGES>
 static cudaError_t launch_fwd_t(const FwdArgs& a, cudaStream_t st) {
     auto kern = forward_kernel<R, FAST, IO, BASE, EDGES>;
@@ -155,7 +136,7 @@ static cudaError_t launch_fwd_r(const FwdArgs& a, bool has_base, cudaStream_t st
 }
 
 template <int R>
-static cudaError_t launch_fwd_d(const FwdArgs& a, bool fast, int io_dtype, bool has_base,
+cudaError_t launch_fwd_d(const FwdArgs& a, bool fast, int io_dtype, bool has_base,
                                 cudaStream_t st) {
     if (io_dtype == QK_BF16) {
         return fast ? launch_fwd_r<R, true, __nv_bfloat16>(a, has_base, st)
@@ -163,21 +144,6 @@ static cudaError_t launch_fwd_d(const FwdArgs& a, bool fast, int io_dtype, bool 
     }
     return fast ? launch_fwd_r<R, true, float>(a, has_base, st)
                 : launch_fwd_r<R, false, float>(a, has_base, st);
-}
-
-cudaError_t launch_forward(const FwdArgs& a, int reps, bool fast, int io_dtype, bool has_base,
-                           cudaStream_t st) {
-    switch (reps) {
-        case 1: return launch_fwd_d<1>(a, fast, io_dtype, has_base, st);
-        case 2: return launch_fwd_d<2>(a, fast, io_dtype, has_base, st);
-        case 3: return launch_fwd_d<3>(a, fast, io_dtype, has_base, st);
-        case 4: return launch_fwd_d<4>(a, fast, io_dtype, has_base, st);
-        case 5: return launch_fwd_d<5>(a, fast, io_dtype, has_base, st);
-        case 6: return launch_fwd_d<6>(a, fast, io_dtype, has_base, st);
-        case 7: return launch_fwd_d<7>(a, fast, io_dtype, has_base, st);
-        case 8: return launch_fwd_d<8>(a, fast, io_dtype, has_base, st);
-        default: return cudaErrorInvalidValue;
-    }
 }
 
 }  // namespace qk

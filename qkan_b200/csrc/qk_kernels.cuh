@@ -52,6 +52,7 @@ struct BwdCfg {
     int grid_b, grid_i;
     int nacc;
     size_t smem;
+    int ru;  // rows a thread interleaves in its inner loop (2 or 4)
 };
 
 struct FwdArgs {

@@ -97,8 +97,12 @@ def layer_forward(x, theta, pw, pb, postw, postb=None, basew=None, mask=None, *,
 def layer_backward(x, theta, pw, pb, postw, postb, basew, mask, gy, *, preact_trainable: bool,
                    fast_measure: bool = True, use_postact_bias: bool = False,
                    want=("x", "theta", "preacts_weight", "preacts_bias", "postact_weights",
-                         "postact_bias", "base_weight")) -> dict:
-    """Gradients of ``sum(y * gy)`` named as the reference's parameters; float32 except ``x``."""
+                         "postact_bias", "base_weight"), out: Optional[dict] = None) -> dict:
+    """Gradients of ``sum(y * gy)`` named as the reference's parameters; float32 except ``x``.
+
+    ``out`` may hold preallocated contiguous destination tensors by name (for example the views
+    of a ``parallel.GradBucket``); the kernels overwrite them, they do not accumulate.
+    """
     lib = _abi.load()
     _require_cuda(x, "x")
     x = x.detach().contiguous()
@@ -108,22 +112,20 @@ def layer_backward(x, theta, pw, pb, postw, postb, basew, mask, gy, *, preact_tr
     desc = _make_desc(x, theta, _flags(preact_trainable, fast_measure, use_postact_bias and postb is not None), pdt)
     O, I, R1, _ = theta.shape
     dev = x.device
-    f32 = dict(dtype=torch.float32, device=dev)
+    shapes = {"x": tuple(x.shape), "theta": (O, I, R1, 2), "preacts_weight": (O, I, R1 - 1),
+              "preacts_bias": (O, I, R1 - 1), "postact_weights": (O, I), "postact_bias": (O, I),
+              "base_weight": (O, I)}
+    given = out or {}
     out = {}
-    if "x" in want:
-        out["x"] = torch.empty_like(x)
-    if "theta" in want:
-        out["theta"] = torch.empty((O, I, R1, 2), **f32)
-    if "preacts_weight" in want:
-        out["preacts_weight"] = torch.empty((O, I, R1 - 1), **f32)
-    if "preacts_bias" in want:
-        out["preacts_bias"] = torch.empty((O, I, R1 - 1), **f32)
-    if "postact_weights" in want:
-        out["postact_weights"] = torch.empty((O, I), **f32)
-    if "postact_bias" in want:
-        out["postact_bias"] = torch.empty((O, I), **f32)
-    if "base_weight" in want:
-        out["base_weight"] = torch.empty((O, I), **f32)
+    for name in want:
+        dt = x.dtype if name == "x" else torch.float32
+        t = given.get(name)
+        if t is None:
+            t = torch.empty(shapes[name], dtype=dt, device=dev)
+        elif (t.dtype != dt or t.device != dev or not t.is_contiguous()
+              or t.numel() != torch.Size(shapes[name]).numel()):
+            raise ValueError(f"out[{name!r}] must be a contiguous {dt} tensor of {shapes[name]} on {dev}")
+        out[name] = t
     with torch.cuda.device(dev):
         nbytes = lib.qk_backward_workspace_bytes(_abi.desc_pointer(desc))
         ws = _workspace(dev, nbytes)
