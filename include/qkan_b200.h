@@ -117,6 +117,39 @@ int qk_pz_postacts_backward(const QkDesc* desc, const void* x, const float* thet
                             float* grad_preacts_weight, float* grad_preacts_bias,
                             void* workspace, size_t workspace_bytes, void* cuda_stream);
 
+/*
+ * Forward for callers that cannot allocate device memory (no counterpart in the
+ * reference; it exists for the hosts this library is embedded in).
+ *
+ * Who needs it: a process whose device memory is wholly owned by another
+ * runtime's pool, or a serving loop in which cudaMalloc - a call that
+ * synchronises the whole device - is banned after start-up. Such a caller has
+ * no workspace to pass, so this variant of qk_pz_forward keeps its scratch in a
+ * fixed array that is part of the library image: qk_noalloc_max_scratch_bytes()
+ * bytes (8 MiB) of device memory on every GPU that loads the library, held
+ * until the process exits. The call itself allocates nothing and frees nothing.
+ *
+ * Limits and rules:
+ *  - the problem must satisfy qk_forward_workspace_bytes(desc) <=
+ *    qk_noalloc_max_scratch_bytes(); larger ones return QK_ERR_WORKSPACE and
+ *    qk_noalloc_last_error() says how many bytes were needed;
+ *  - the first call on each device looks the array's address up (a one-time
+ *    runtime query); make that first call during start-up, before any stream
+ *    capture is begun;
+ *  - all calls on a device share the one array and it keeps whatever the last
+ *    call left there. The forward rewrites everything it reads, so no clearing
+ *    is needed, but two calls that can overlap on the GPU (different streams
+ *    with no ordering between them) race on it: keep them on one stream or
+ *    order them with events.
+ * Inputs, outputs and results are those of qk_pz_forward.
+ */
+size_t qk_noalloc_max_scratch_bytes(void);
+const char* qk_noalloc_last_error(void);
+int qk_pz_forward_noalloc(const QkDesc* desc, const void* x, const float* theta,
+                          const float* preacts_weight, const float* preacts_bias,
+                          const void* postact_weights, const void* postact_bias,
+                          const void* base_weight, const void* mask, void* y, void* cuda_stream);
+
 #ifdef __cplusplus
 }
 #endif

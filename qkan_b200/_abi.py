@@ -37,6 +37,9 @@ SYMBOLS = {
     "qk_pz_backward": (c_int, [_P] * 17 + [_P, c_size_t, _P]),
     "qk_pz_postacts_forward": (c_int, [_P] * 6 + [_P, c_size_t, _P]),
     "qk_pz_postacts_backward": (c_int, [_P] * 10 + [_P, c_size_t, _P]),
+    "qk_noalloc_max_scratch_bytes": (c_size_t, []),
+    "qk_noalloc_last_error": (c_char_p, []),
+    "qk_pz_forward_noalloc": (c_int, [_P] * 10 + [_P]),
 }
 
 
