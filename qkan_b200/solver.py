@@ -1,0 +1,79 @@
+"""The kernels as a solver plug-in in the reference's sense.
+
+The reference dispatches through a string-keyed registry of callables
+``solver(x, theta, preacts_weight, preacts_bias, reps, **kwargs) -> (B, O, I)``
+(``src/qkan/solver/_base.py:29-70``; call site ``src/qkan/qkan.py:699-714``).
+``B200Solver`` implements that contract on the CUDA kernels; a small registry with the
+same three functions lives here, and ``register_with_reference()`` adds the solver to
+the reference's own registry when that package is installed next to this one.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import functional as qf
+
+_PZ = ("pz_encoding", "pz")
+
+
+class B200Solver:
+    """``solver="b200"``: per-edge activations of the pz ansatz on the sm_100a kernels."""
+
+    name = "b200"
+
+    def __call__(self, x, theta, preacts_weight, preacts_bias, reps, **kwargs) -> torch.Tensor:
+        ansatz = kwargs.get("ansatz", "pz_encoding")
+        if callable(ansatz) or ansatz not in _PZ:
+            raise NotImplementedError(f"the b200 solver implements 'pz_encoding' only, got {ansatz!r}")
+        trainable = kwargs.get("preacts_trainable", False)
+        fast = kwargs.get("fast_measure", True)
+        batch, in_dim = x.shape
+        out_dim = kwargs.get("out_dim", in_dim)
+        # group broadcasting as the reference solvers do it (src/qkan/solver/exact.py:68-86)
+        if theta.dim() != 4:
+            theta = theta.unsqueeze(0)
+        if theta.shape[1] != in_dim or theta.shape[0] != out_dim:
+            rep_in = in_dim // theta.shape[1] + 1
+            rep_out = out_dim if theta.shape[0] == 1 else 1
+            theta = theta.repeat(rep_out, rep_in, 1, 1)[:, :in_dim]
+        if preacts_weight.dim() != 3:
+            preacts_weight, preacts_bias = preacts_weight.unsqueeze(0), preacts_bias.unsqueeze(0)
+        if preacts_weight.shape[1] != in_dim or preacts_weight.shape[0] != out_dim:
+            rep_in = in_dim // preacts_weight.shape[1] + 1
+            rep_out = out_dim if preacts_weight.shape[0] == 1 else 1
+            preacts_weight = preacts_weight.repeat(rep_out, rep_in, 1)[:, :in_dim]
+            preacts_bias = preacts_bias.repeat(rep_out, rep_in, 1)[:, :in_dim]
+        if theta.shape[2] != reps + 1:
+            raise ValueError(f"theta holds {theta.shape[2] - 1} repetitions, reps={reps}")
+        return qf.qkan_postacts(x, theta, preacts_weight, preacts_bias, preact_trainable=trainable,
+                                fast_measure=fast)
+
+
+_REGISTRY: dict = {}
+
+
+def register(solver):
+    """Register a solver instance under its ``name`` (``src/qkan/solver/_base.py:57-60``)."""
+    _REGISTRY[solver.name] = solver
+    return solver
+
+
+def get_solver(name: str):
+    return _REGISTRY[name]
+
+
+def get_registry() -> dict:
+    return _REGISTRY
+
+
+register(B200Solver())
+
+
+def register_with_reference() -> bool:
+    """Add the solver to the reference package's registry; False when that package is absent."""
+    try:
+        from qkan.solver import register as ref_register  # type: ignore
+    except Exception:
+        return False
+    ref_register(get_solver("b200"))
+    return True

@@ -1,0 +1,118 @@
+"""The reference-facing classes on the GPU: QKANLayer / QKAN through autograd against golden values."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle
+from qkan_b200 import QKAN, QKANLayer, get_solver
+from tests.util import GOLDEN, GRAD_NAMES, TOL_BF16, TOL_F32, case_inputs, golden_layer_cases, nerr
+
+pytestmark = pytest.mark.gpu
+
+
+def _layer_from_case(case, p_dim=4):
+    B, I, O, R = (int(v) for v in case["dims"])
+    cfg = case["cfg"]
+    layer = QKANLayer(I, O, reps=R, device="cuda", preact_trainable=cfg["preact_trainable"],
+                      postact_weight_trainable=True, postact_bias_trainable=cfg["use_postact_bias"],
+                      ba_trainable=case["base"], fast_measure=cfg["fast_measure"], p_dim=p_dim)
+    with torch.no_grad():
+        for name in ("theta", "preacts_weight", "preacts_bias", "postact_weights", "postact_bias",
+                     "base_weight", "mask"):
+            src = torch.as_tensor(case["in_" + name], dtype=torch.float32, device="cuda")
+            getattr(layer, name).copy_(src.reshape(getattr(layer, name).shape))
+    layer._mask_is_identity = not case["masked"]
+    return layer
+
+
+@pytest.mark.parametrize("p_dim", [4, 2])
+@pytest.mark.parametrize("case", golden_layer_cases(), ids=lambda c: c["name"])
+def test_layer_autograd_matches_reference(case, p_dim):
+    layer = _layer_from_case(case, p_dim).train()
+    x = torch.as_tensor(case["in_x"], dtype=torch.float32, device="cuda").requires_grad_(True)
+    gy = torch.as_tensor(case["in_gy"], dtype=torch.float32, device="cuda")
+    y = layer(x)
+    (y * gy).sum().backward()
+    assert nerr(y.detach().cpu().numpy(), case["y"]) <= TOL_F32
+    assert nerr(x.grad.cpu().numpy(), case["g_x"]) <= TOL_F32
+    for name in GRAD_NAMES[1:]:
+        p = getattr(layer, name)
+        ref = case["g_" + name]
+        if p.grad is None:
+            assert not p.requires_grad
+            continue
+        assert nerr(p.grad.reshape(ref.shape).cpu().numpy(), ref) <= TOL_F32, name
+    layer.eval()
+    with torch.no_grad():
+        assert nerr(layer(x).cpu().numpy(), case["y"]) <= TOL_F32
+        full = layer.forward_no_sum(x)
+    assert nerr(full.sum(dim=2).cpu().numpy(), case["y"]) <= TOL_F32
+
+
+def test_fit_case_initial_loss_and_gradients_match_reference():
+    gold = np.load(f"{GOLDEN}/fit_case.npz")
+    xs = torch.as_tensor(gold["train_input"], device="cuda")
+    ys = torch.as_tensor(gold["train_label"], device="cuda")
+    for tag, ba in (("ba", True), ("noba", False)):
+        model = QKAN([1, 1], reps=3, seed=0, device="cuda", preact_trainable=True,
+                     postact_weight_trainable=True, postact_bias_trainable=True, ba_trainable=ba)
+        model.train()
+        pred = model(xs)
+        loss = torch.nn.functional.mse_loss(pred, ys)
+        loss.backward()
+        assert nerr(pred.detach().cpu().numpy(), gold[f"{tag}/pred0"]) <= TOL_F32
+        assert abs(loss.item() - float(gold[f"{tag}/loss0"])) <= 1e-5 * float(gold[f"{tag}/loss0"])
+        for name, p in model.named_parameters():
+            key = f"{tag}/grad/{name}"
+            if key in gold.files:
+                assert nerr(p.grad.cpu().numpy(), gold[key]) <= 2 * TOL_F32, name
+
+
+def test_fit_case_lbfgs_training_converges_like_the_reference():
+    """LBFGS amplifies rounding, so the criterion is the final loss within a factor 1.5 of the reference's."""
+    gold = np.load(f"{GOLDEN}/fit_case.npz")
+    dataset = {k: torch.as_tensor(gold[k], device="cuda") for k in
+               ("train_input", "train_label", "test_input", "test_label")}
+    model = QKAN([1, 1], reps=3, seed=0, device="cuda", preact_trainable=True,
+                 postact_weight_trainable=True, postact_bias_trainable=True, ba_trainable=True)
+    opt = torch.optim.LBFGS(model.parameters(), lr=5e-2)
+    res = model.train_(dataset, optimizer=opt, steps=100, verbose=False)
+    assert set(res) == {"train_loss", "test_loss", "reg"} and len(res["train_loss"]) == 100
+    assert abs(float(res["train_loss"][0]) - gold["ba/train_loss"][0]) <= 1e-3 * gold["ba/train_loss"][0]
+    assert float(res["train_loss"][-1]) <= 1.5 * float(gold["ba/train_loss"][-1])
+    assert float(res["test_loss"][-1]) <= 1.5 * float(gold["ba/test_loss"][-1])
+
+
+def test_grouped_theta_and_solver_contract():
+    torch.manual_seed(0)
+    layer = QKANLayer(6, 4, reps=2, group=3, device="cuda", seed=2, preact_trainable=True,
+                      postact_weight_trainable=True, ba_trainable=False)
+    x = torch.rand(9, 6, device="cuda") * 2 - 1
+    y = layer(x)
+    y.square().sum().backward()
+    theta, pw, pb = (t.detach().double().cpu().numpy() for t in layer._expanded())
+    ones = np.ones((4, 6))
+    y_ref = oracle.forward(x.cpu().numpy(), theta, pw, pb, ones, preact_trainable=True)
+    assert nerr(y.detach().cpu().numpy(), y_ref) <= TOL_F32
+    g = oracle.backward(x.cpu().numpy(), theta, pw, pb, ones, None, None, None, 2 * y_ref, preact_trainable=True)
+    g_group = np.stack([g["theta"][:, k::3].sum(axis=(0, 1)) for k in range(3)])
+    assert nerr(layer.theta.grad.cpu().numpy(), g_group) <= TOL_F32
+    pa = get_solver("b200")(x, layer.theta, layer.preacts_weight, layer.preacts_bias, 2,
+                            preacts_trainable=True, fast_measure=True, out_dim=4, group=(3,))
+    assert pa.shape == (9, 4, 6)
+    assert nerr(pa.sum(dim=2).detach().cpu().numpy(), y_ref) <= TOL_F32
+
+
+def test_mlp_with_bf16_activations_and_sequence_axis():
+    model = QKAN([16, 24, 8], reps=2, seed=4, device="cuda", p_dtype=torch.bfloat16, c_dtype=torch.bfloat16)
+    x = (torch.rand(2, 5, 16, device="cuda") * 2 - 1).to(torch.bfloat16)
+    y = model(x)
+    assert y.shape == (2, 5, 8) and y.dtype == torch.bfloat16
+    # float32 twin with the same (bf16-rounded) parameters
+    twin = QKAN([16, 24, 8], reps=2, seed=4, device="cuda")
+    twin.load_state_dict({k: v.float() for k, v in model.state_dict().items()})
+    y32 = twin(x.float())
+    assert nerr(y.float().cpu().numpy(), y32.detach().cpu().numpy()) <= 2 * TOL_BF16
+    y.float().sum().backward()
+    assert all(p.grad is not None and p.grad.dtype == torch.bfloat16
+               for p in model.parameters() if p.requires_grad)

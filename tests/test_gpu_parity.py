@@ -117,9 +117,5 @@ def test_empty_batch_and_bad_arguments():
     assert float(g0["theta"].abs().max()) == 0.0
     with pytest.raises(ValueError):
         F.layer_forward(torch.zeros((4, 5), device="cuda"), th, pw, pb, postw, **cfg)
-    with pytest.raises(NotImplementedError):
-        th9 = torch.zeros((2, 3, 10, 2), device="cuda")
-        F.layer_forward(_dev(p["x"]), th9, torch.zeros((2, 3, 9), device="cuda"),
-                        torch.zeros((2, 3, 9), device="cuda"), postw, **cfg)
     with pytest.raises(RuntimeError):
         F.layer_forward(torch.zeros((4, 3)), th, pw, pb, postw, **cfg)
