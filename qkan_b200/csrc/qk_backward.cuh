@@ -31,12 +31,12 @@ __device__ __forceinline__ float edge_backward(const EdgeFwd<R>& e, float bw, fl
     // w = v x a, a = cotangent of the final Bloch vector (its z component of w is 0)
     float wx, wy, wz;
     if (FAST) {
+        // a = (q vx, q vy, az) with q = -gp r^3 vz / (2 rho); then v x a = (vy k, -vx k, 0), k = az - vz q
         const float az = gp * r;
-        const float t = az * r * r;
-        const float q = (t * vz) * (-0.5f * inv_rho);
-        const float ax = q * vx, ay = q * vy;
-        wx = fmaf(vy, az, -(vz * ay));
-        wy = fmaf(vz, ax, -(vx * az));
+        const float t = az * (r * r);
+        const float k = fmaf((0.5f * vz) * vz, t * inv_rho, az);
+        wx = vy * k;
+        wy = -(vx * k);
     } else {
         wx = vy * gp;
         wy = -(vx * gp);
@@ -78,7 +78,8 @@ constexpr int kGyChunk = 8;  // outputs whose grad_y columns are staged together
 template <int R, bool FAST, typename IO, bool BASE, bool EDGES, int RU>
 __global__ void __launch_bounds__(512) backward_kernel(BwdArgs a) {
     constexpr int NACC = acc_rows(R, BASE);
-    constexpr int ROW = BASE ? 128 : 64;  // floats per tile row: x | grad_x [| silu | silu']
+    // floats per tile row: 32 (x, grad_x) pairs [+ 32 (silu, silu') pairs]; a pair is one 64-bit access
+    constexpr int ROW = BASE ? 128 : 64;
     extern __shared__ __align__(16) float smem[];
     const int groups = a.cfg.groups, rpg = a.cfg.rpg, tb = a.cfg.tb;
     float* xg_s = smem;                                  // [tb][ROW]
@@ -93,18 +94,16 @@ __global__ void __launch_bounds__(512) backward_kernel(BwdArgs a) {
     const IO* __restrict__ x = static_cast<const IO*>(a.x);
     const IO* __restrict__ gsrc = static_cast<const IO*>(EDGES ? a.gpostacts : a.gy);
     const int row0 = grp * rpg;
-    float* const my = xg_s + (size_t)row0 * ROW + lane;  // this thread's column of its group's rows
+    float* const my = xg_s + (size_t)row0 * ROW + 2 * lane;  // this thread's column of its group's rows
 
     for (int j = 0; j < rpg; ++j) {
         const int row = row0 + j;
         float v = 0.f;
         if (b0 + row < a.batch && i < a.in_dim) v = ld_as_float(x + (size_t)(b0 + row) * a.in_dim + i);
-        my[j * ROW] = v;
-        my[j * ROW + 32] = 0.f;
+        *reinterpret_cast<float2*>(my + j * ROW) = make_float2(v, 0.f);
         if (BASE) {
             float sg = sigmoid_f(v);
-            my[j * ROW + 64] = v * sg;
-            my[j * ROW + 96] = sg * (1.f + v * (1.f - sg));
+            *reinterpret_cast<float2*>(my + j * ROW + 64) = make_float2(v * sg, sg * (1.f + v * (1.f - sg)));
         }
     }
     // a thread only ever touches its own column of its own group's rows: no barrier needed for xg_s
@@ -137,12 +136,18 @@ __global__ void __launch_bounds__(512) backward_kernel(BwdArgs a) {
             float* p = my;
 #pragma unroll 1
             for (int j = 0; j < rpg; j += RU, p += RU * ROW) {
-                float xv[RU], g[RU], sl[RU], dsl[RU];
+                float xv[RU], gxo[RU], g[RU], sl[RU], dsl[RU];
 #pragma unroll
                 for (int u = 0; u < RU; ++u) {
-                    xv[u] = p[u * ROW];
-                    sl[u] = BASE ? p[u * ROW + 64] : 0.f;
-                    dsl[u] = BASE ? p[u * ROW + 96] : 0.f;
+                    const float2 xg = *reinterpret_cast<const float2*>(p + u * ROW);
+                    xv[u] = xg.x;
+                    gxo[u] = xg.y;
+                    sl[u] = dsl[u] = 0.f;
+                    if (BASE) {
+                        const float2 sd = *reinterpret_cast<const float2*>(p + u * ROW + 64);
+                        sl[u] = sd.x;
+                        dsl[u] = sd.y;
+                    }
                     if (EDGES) {
                         const int b = b0 + row0 + j + u;
                         g[u] = 0.f;
@@ -170,7 +175,7 @@ __global__ void __launch_bounds__(512) backward_kernel(BwdArgs a) {
                 for (int u = 0; u < RU; ++u) {
                     float gx = edge_backward<R, FAST, BASE, EDGES, NACC>(e, bw, xv[u], g[u], sl[u],
                                                                          dsl[u], acc);
-                    p[u * ROW + 32] += gx;
+                    p[u * ROW + 1] = gxo[u] + gx;
                 }
             }
 
@@ -193,7 +198,7 @@ __global__ void __launch_bounds__(512) backward_kernel(BwdArgs a) {
         for (int j = 0; j < rpg; ++j) {
             const int row = row0 + j;
             if (b0 + row < a.batch && i < a.in_dim)
-                st_from_float(gx + (size_t)(b0 + row) * a.in_dim + i, my[j * ROW + 32]);
+                st_from_float(gx + (size_t)(b0 + row) * a.in_dim + i, my[j * ROW + 1]);
         }
     }
 }

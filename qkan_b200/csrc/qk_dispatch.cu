@@ -49,9 +49,18 @@ BwdCfg choose_bwd_cfg(const QkDesc& d, bool base) {
     const int nacc = acc_rows(d.reps, base);
     const int grid_i = (d.in_dim + 31) / 32;
     const size_t budget = 200 * 1024;
-    static const int cand[][2] = {{16, 32}, {16, 16}, {8, 32}, {8, 16}, {16, 8}, {8, 8}, {4, 8}, {2, 8}, {1, 8}};
+    // (row groups = warps per CTA, rows per group), largest tile first; 8x32 runs two CTAs per SM
+    static const int cand[][2] = {{8, 32}, {8, 16}, {4, 16}, {8, 8}, {4, 8}, {2, 8}, {1, 8}};
     BwdCfg best{};
     long best_ctas = -1;
+    const int force_groups = tune_int("QK_BWD_GROUPS", 0), force_rpg = tune_int("QK_BWD_RPG", 0);
+    if (force_groups > 0 && force_rpg > 0) {  // developer override of the tile shape
+        const int tb = force_groups * force_rpg;
+        size_t smem = (size_t)tb * 32 * 4 * (base ? 4 : 2) + (size_t)kGyChunkHost * tb * 4 +
+                      (size_t)2 * force_groups * nacc * 32 * 4;
+        return BwdCfg{force_groups, force_rpg, tb, (d.batch + tb - 1) / tb, grid_i, nacc, smem,
+                      tune_int("QK_BWD_RU", 4)};
+    }
     for (auto& c : cand) {
         const int groups = c[0], rpg = c[1], tb = groups * rpg;
         size_t smem = (size_t)tb * 32 * 4 * (base ? 4 : 2) + (size_t)kGyChunkHost * tb * 4 +
@@ -59,7 +68,7 @@ BwdCfg choose_bwd_cfg(const QkDesc& d, bool base) {
         if (smem > budget) continue;
         const int grid_b = (d.batch + tb - 1) / tb;
         const long ctas = (long)grid_b * grid_i;
-        BwdCfg cur{groups, rpg, tb, grid_b, grid_i, nacc, smem, tune_int("QK_BWD_RU", 2)};
+        BwdCfg cur{groups, rpg, tb, grid_b, grid_i, nacc, smem, tune_int("QK_BWD_RU", 4)};
         if (ctas >= 296) return cur;  // first (largest) tile that still fills the machine twice
         if (ctas > best_ctas) {
             best = cur;

