@@ -46,6 +46,11 @@ def work_per_edge(reps: int):
 
 SM_COUNT, FP32_LANES, SFU_LANES, NOMINAL_GHZ = 148, 128, 16, 1.965
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one backward_kernel launch, from the ncu capture of a
+# 16384-row case (52.5 MB + 161.9 MB) scaled by 4 to the 65536-row batch; the traffic is proportional to
+# the batch (activations and per-tile partials). See profiles/forward_backward_kernels_batch16384.md.
+BACKWARD_DRAM_BYTES_PER_LAUNCH = 4 * (52_529_152 + 161_943_552)
+
 
 def issue_roofline_seconds(edges: float, reps: int, which: str, ghz: float = NOMINAL_GHZ) -> float:
     wf, wm = work_per_edge(reps)[which]
@@ -142,6 +147,7 @@ def cpu_baseline(sample_rows: int, repeats: int = 1):
     """Times the CPU port of the reference algorithm (oracle/, float32) on `sample_rows` rows."""
     from oracle import oracle
 
+    oracle.use_all_cores()
     p = make_problem_numpy(1234, sample_rows)
     args = [p["x"], p["theta"], p["pw"], p["pb"], p["postw"], p["postb"], None, None]
     cfg = dict(preact_trainable=True, fast_measure=True, use_postact_bias=True, dtype=np.float32)
@@ -337,10 +343,8 @@ def run_b200(args):
                     "peak_gbs": peaks["hbm_gbs"], "peak_kind": peak_kind},
             "traffic": None,
         }
-        prof = os.path.join(ROOT, "profiles", "traffic.json")
-        if os.path.exists(prof):
-            with open(prof) as fh:
-                roofline["traffic"] = json.load(fh).get("dram_bytes_per_step")
+        if rows == B_PER_GPU:
+            roofline["traffic"] = BACKWARD_DRAM_BYTES_PER_LAUNCH
         cpu = None
         if world == 1 and not args.no_cpu_baseline:
             cpu, _ = cpu_baseline(args.cpu_rows)

@@ -38,6 +38,16 @@ def num_threads() -> int:
     return int(lib().qkan_oracle_num_threads_f32())
 
 
+def use_all_cores() -> int:
+    """Run the OpenMP loops on every core this process may use (overrides OMP_NUM_THREADS=1 set by launchers)."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:  # pragma: no cover
+        n = os.cpu_count() or 1
+    lib().qkan_oracle_set_num_threads_f32(n)
+    return num_threads()
+
+
 def _flags(preact_trainable: bool, fast_measure: bool, use_postact_bias: bool) -> int:
     return ((PREACT_TRAINABLE if preact_trainable else 0) | (FAST_MEASURE if fast_measure else 0)
             | (USE_POSTACT_BIAS if use_postact_bias else 0))

@@ -312,6 +312,15 @@ int FN(qkan_oracle_backward)(int B, int I, int O, int R, unsigned flags, const r
     return 0;
 }
 
+/* Launchers such as torchrun export OMP_NUM_THREADS=1; the baseline timing asks for all cores explicitly. */
+void FN(qkan_oracle_set_num_threads)(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 int FN(qkan_oracle_num_threads)(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();
