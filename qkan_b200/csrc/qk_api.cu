@@ -3,6 +3,7 @@
 // allocation, no synchronisation.
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 
 #include "qk_kernels.cuh"
 
@@ -126,6 +127,9 @@ int run_forward(const QkDesc* desc, const void* x, const float* theta, const flo
     f.out_dim = d.out_dim;
     f.ipad = l.ipad;
     f.cfg = qk::choose_fwd_cfg(d, edges, has_base);
+    if (getenv("QK_DEBUG"))
+        fprintf(stderr, "[qk] forward B=%d I=%d O=%d R=%d: tile %d rows x %d outputs, grid %d x %d, smem %zu\n",
+                d.batch, d.in_dim, d.out_dim, d.reps, f.cfg.tb, f.cfg.ot, f.cfg.grid_b, f.cfg.grid_o, f.cfg.smem);
     f.x = x;
     f.table = p.table;
     f.bias = p.bias;
@@ -203,6 +207,10 @@ int run_backward(const QkDesc* desc, const void* x, const float* theta, const fl
     b.out_dim = d.out_dim;
     b.ipad = l.ipad;
     b.cfg = qk::choose_bwd_cfg(d, has_base);
+    if (getenv("QK_DEBUG"))
+        fprintf(stderr, "[qk] backward B=%d I=%d O=%d R=%d: %d groups x %d rows, grid %d x %d, smem %zu, ru %d\n",
+                d.batch, d.in_dim, d.out_dim, d.reps, b.cfg.groups, b.cfg.rpg, b.cfg.grid_b, b.cfg.grid_i,
+                b.cfg.smem, b.cfg.ru);
     b.x = x;
     b.gy = gy;
     b.gpostacts = gpostacts;

@@ -1,6 +1,7 @@
 // Tile-shape selection and the dispatch on the repetition count. The kernels
 // themselves are instantiated once per R in qk_forward_inst.cu / qk_backward_inst.cu.
 #include <cstdlib>
+#include <initializer_list>
 
 #include "qk_kernels.cuh"
 
@@ -25,59 +26,94 @@ cudaError_t launch_bwd_d(const BwdArgs& a, bool fast, int io_dtype, bool has_bas
 QK_DECL(1) QK_DECL(2) QK_DECL(3) QK_DECL(4) QK_DECL(5) QK_DECL(6) QK_DECL(7) QK_DECL(8)
 #undef QK_DECL
 
-FwdCfg choose_fwd_cfg(const QkDesc& d, bool edges, bool base) {
-    FwdCfg c;
-    const int ipad = round_up(d.in_dim, 32);
-    c.threads = 512;
-    c.ich = ipad < 256 ? ipad : 256;
-    c.ot = d.out_dim < 256 ? d.out_dim : 256;
-    c.tb = 64;
-    // small problems: shrink the tile until the grid covers the machine twice
-    auto ctas = [&](int tb, int ot) {
-        return (long)((d.batch + tb - 1) / tb) * ((d.out_dim + ot - 1) / ot);
-    };
-    if (ctas(c.tb, c.ot) < 296) c.tb = 32;
-    while (ctas(c.tb, c.ot) < 296 && c.ot > 16) c.ot = (c.ot + 1) / 2;
-    c.grid_b = (d.batch + c.tb - 1) / c.tb;
-    c.grid_o = (d.out_dim + c.ot - 1) / c.ot;
-    // x tile + y tile + (with the base term) silu(x) tile
-    c.smem = (size_t)c.tb * c.ich * 4 * (base ? 2 : 1) + (edges ? 0 : (size_t)c.ot * (c.tb + 1) * 4);
-    return c;
-}
+constexpr int kSmCount = 148;
+constexpr size_t kSmemPerSm = 227 * 1024;
 
-BwdCfg choose_bwd_cfg(const QkDesc& d, bool base) {
-    const int nacc = acc_rows(d.reps, base);
-    const int grid_i = (d.in_dim + 31) / 32;
-    const size_t budget = 200 * 1024;
-    // (row groups = warps per CTA, rows per group), largest tile first; 8x32 runs two CTAs per SM
-    static const int cand[][2] = {{8, 32}, {8, 16}, {4, 16}, {8, 8}, {4, 8}, {2, 8}, {1, 8}};
-    BwdCfg best{};
-    long best_ctas = -1;
-    const int force_groups = tune_int("QK_BWD_GROUPS", 0), force_rpg = tune_int("QK_BWD_RPG", 0);
-    if (force_groups > 0 && force_rpg > 0) {  // developer override of the tile shape
-        const int tb = force_groups * force_rpg;
-        size_t smem = (size_t)tb * 32 * 4 * (base ? 4 : 2) + (size_t)kGyChunkHost * tb * 4 +
-                      (size_t)2 * force_groups * nacc * 32 * 4;
-        return BwdCfg{force_groups, force_rpg, tb, (d.batch + tb - 1) / tb, grid_i, nacc, smem,
-                      tune_int("QK_BWD_RU", 4)};
-    }
-    for (auto& c : cand) {
-        const int groups = c[0], rpg = c[1], tb = groups * rpg;
-        size_t smem = (size_t)tb * 32 * 4 * (base ? 4 : 2) + (size_t)kGyChunkHost * tb * 4 +
-                      (size_t)2 * groups * nacc * 32 * 4;
-        if (smem > budget) continue;
-        const int grid_b = (d.batch + tb - 1) / tb;
-        const long ctas = (long)grid_b * grid_i;
-        BwdCfg cur{groups, rpg, tb, grid_b, grid_i, nacc, smem, tune_int("QK_BWD_RU", 4)};
-        if (ctas >= 296) return cur;  // first (largest) tile that still fills the machine twice
-        if (ctas > best_ctas) {
-            best = cur;
-            best_ctas = ctas;
+// Tile shapes are chosen with a small cost model: the busiest SM gets ceil(CTAs / 148) CTAs, a
+// CTA's time grows with the edges x rows it owns plus its per-edge set-up, and too few resident
+// warps cannot keep the issue slots busy. The largest tile wins ties (fewest partials / re-reads).
+FwdCfg choose_fwd_cfg(const QkDesc& d, bool edges, bool base) {
+    const int ipad = round_up(d.in_dim, 32);
+    FwdCfg best{};
+    double best_cost = -1.0;
+    for (int tb : {64, 32}) {
+        for (int ot = 256; ot >= 1; ot /= 2) {
+            FwdCfg c{};
+            c.threads = 512;
+            c.ich = ipad < 256 ? ipad : 256;
+            c.tb = tb;
+            c.ot = d.out_dim < ot ? d.out_dim : ot;
+            if (c.ot < 16 && c.ot < d.out_dim) continue;  // fewer outputs than warps: idle warps
+            c.grid_b = (d.batch + tb - 1) / tb;
+            c.grid_o = (d.out_dim + c.ot - 1) / c.ot;
+            c.smem = (size_t)tb * c.ich * 4 * (base ? 2 : 1) + (edges ? 0 : (size_t)c.ot * (tb + 1) * 4);
+            if (c.smem > 200 * 1024) continue;
+            const long ctas = (long)c.grid_b * c.grid_o;
+            const long per_sm = (ctas + kSmCount - 1) / kSmCount;  // one CTA of 16 warps per SM at a time
+            // constant loads per (o, 32 columns); warps that own a single output each stay in step
+            // between barriers and expose that load latency together
+            const double per_warp = c.ot / 16.0 < 1.0 ? 1.0 : c.ot / 16.0;
+            const double setup = 1.0 + (0.6 + 8.0 / per_warp) / tb;
+            const double cost = (double)per_sm * tb * c.ot * setup;
+            if (best_cost < 0 || cost < best_cost * 0.999) {
+                best = c;
+                best_cost = cost;
+            }
         }
     }
     return best;
 }
 
+BwdCfg choose_bwd_cfg(const QkDesc& d, bool base) {
+    const int nacc = acc_rows(d.reps, base);
+    const int grid_i = (d.in_dim + 31) / 32;
+    const int ru = tune_int("QK_BWD_RU", 4);
+    auto make = [&](int groups, int rpg) {
+        const int tb = groups * rpg;
+        size_t smem = (size_t)tb * 32 * 4 * (base ? 4 : 2) + (size_t)kGyChunkHost * tb * 4 +
+                      (size_t)2 * groups * nacc * 32 * 4;
+        return BwdCfg{groups, rpg, tb, (d.batch + tb - 1) / tb, grid_i, nacc, smem, ru};
+    };
+    const int force_groups = tune_int("QK_BWD_GROUPS", 0), force_rpg = tune_int("QK_BWD_RPG", 0);
+    if (force_groups > 0 && force_rpg > 0) return make(force_groups, force_rpg);  // developer override
+    // (row groups = warps per CTA, rows per group), largest tile first
+    static const int cand[][2] = {{8, 32}, {8, 16}, {4, 32}, {4, 16}, {8, 8}, {2, 32}, {4, 8}, {2, 16}, {2, 8}, {1, 8}};
+    const int regs_est = 34 + 11 * d.reps > 255 ? 255 : 34 + 11 * d.reps;
+    const int ipad = round_up(d.in_dim, 32);
+    // seconds per (row x 32 columns x output) on one SM: ~(28 R + 20) instructions at 0.72 IPC x 4 schedulers
+    const double t_unit = (28.0 * d.reps + 20.0) / (4 * 0.72 * 1.965e9);
+    const double partial_cap = 8.0 * 1024 * 1024 * 1024;  // bytes of per-tile partials we are willing to hold
+    BwdCfg best{};
+    double best_cost = -1.0;
+    for (int pass = 0; pass < 2 && best_cost < 0; ++pass) {
+        for (auto& c : cand) {
+            BwdCfg cur = make(c[0], c[1]);
+            if (cur.smem > 200 * 1024) continue;
+            const double partial_bytes = (double)cur.grid_b * d.out_dim * nacc * ipad * 4.0;
+            if (pass == 0 && partial_bytes > partial_cap) continue;  // second pass lifts the cap if nothing fits
+            const long ctas = (long)cur.grid_b * grid_i;
+            long resident = (long)(kSmemPerSm / (cur.smem + 1024));
+            const long by_regs = 65536 / ((long)regs_est * cur.groups * 32);
+            if (by_regs < resident) resident = by_regs;
+            if (resident < 1) resident = 1;
+            const long per_sm = (ctas + kSmCount - 1) / kSmCount;
+            const long live = per_sm < resident ? per_sm : resident;
+            const double warps = (double)live * cur.groups;
+            const double occupancy =
+                warps >= 16 ? 1.0 : (warps >= 8 ? 1.0 + 0.04 * (16 - warps) : 1.32 + 0.2 * (8 - warps));
+            const double setup = 1.0 + 0.09 * 32.0 / cur.rpg;       // per-edge set-up and reduction per row
+            const double small_cta = 1.0 + 0.02 * (8.0 / cur.groups - 1.0);
+            const double compute = (double)per_sm * cur.tb * d.out_dim * t_unit * setup * occupancy * small_cta;
+            const double partials = 2.0 * partial_bytes / 6.0e12;  // written here, read by finish_grads
+            const double cost = compute + partials;
+            if (best_cost < 0 || cost < best_cost * 0.999) {
+                best = cur;
+                best_cost = cost;
+            }
+        }
+    }
+    return best;
+}
 
 cudaError_t launch_forward(const FwdArgs& a, int reps, bool fast, int io_dtype, bool has_base,
                            cudaStream_t st) {
