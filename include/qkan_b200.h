@@ -1,5 +1,5 @@
 /*
- * qkan_b200 — C ABI of the sm_100a QKANLayer kernels (pz_encoding ansatz).
+ * qkan_b200 — C ABI of the sm_100a QKANLayer kernels (pz_encoding, rpz_encoding and real ansaetze).
  *
  * Every entry point takes plain device pointers and sizes, launches on the
  * stream it is given, never synchronises, never allocates and never throws.
@@ -8,7 +8,7 @@
  *
  * Tensor layouts are the reference's natural-rank, row-major layouts
  * (src/qkan/qkan.py:259-347):
- *   x (B,I)  y (B,O)  theta (O,I,R+1,2)  preacts_weight/bias (O,I,R)
+ *   x (B,I)  y (B,O)  theta (O,I,R+1,2) [see QkAnsatz]  preacts_weight/bias (O,I,R)
  *   postact_weights / postact_bias / base_weight / mask (O,I)
  * theta and preacts are always float32. x, y and their gradients use
  * QkDesc.io_dtype; the four (O,I) tensors use QkDesc.param_dtype. All
@@ -24,14 +24,26 @@
 extern "C" {
 #endif
 
-#define QK_ABI_VERSION 1
+#define QK_ABI_VERSION 2
 
 enum QkDtype { QK_F32 = 0, QK_BF16 = 1 };
+
+/*
+ * Circuit family (QKANLayer `ansatz=`). theta layouts follow src/qkan/qkan.py:259-274:
+ *   QK_ANSATZ_PZ   "pz_encoding"  theta (O,I,R+1,2)   src/qkan/solver/exact.py:90-134
+ *   QK_ANSATZ_RPZ  "rpz_encoding" theta (O,I,R+1,1)   src/qkan/solver/exact.py:136-168
+ *                  (always encodes preacts_weight*x + preacts_bias, whatever QK_PREACT_TRAINABLE says)
+ *   QK_ANSATZ_REAL "real"         theta (O,I,R,1)     src/qkan/solver/exact.py:216-257
+ */
+enum QkAnsatz { QK_ANSATZ_PZ = 0, QK_ANSATZ_RPZ = 1, QK_ANSATZ_REAL = 2 };
 
 enum QkFlags {
     QK_PREACT_TRAINABLE = 1u, /* encode pw*x+pb; otherwise x itself (exact.py:87,121-124) */
     QK_FAST_MEASURE = 2u,     /* |a|-|b| readout; otherwise |a|^2-|b|^2 (torch_qc.py:261-277) */
-    QK_USE_POSTACT_BIAS = 4u  /* add postact_bias before the weight (qkan.py:776-783) */
+    QK_USE_POSTACT_BIAS = 4u, /* add postact_bias before the weight (qkan.py:776-783) */
+    QK_PRECISE_MATH = 8u      /* sin/cos/sqrt by the full-precision routines instead of the special-function
+                                 unit (float32 I/O only): ~1 ulp and smooth in the argument, as torch's own
+                                 sin/cos in the reference are; meant for small fits driven by LBFGS */
 };
 
 enum QkError {
@@ -46,11 +58,11 @@ typedef struct QkDesc {
     int32_t batch;       /* B */
     int32_t in_dim;      /* I */
     int32_t out_dim;     /* O */
-    int32_t reps;        /* R >= 1 */
+    int32_t reps;        /* 1 <= R <= 16 */
     int32_t io_dtype;    /* QkDtype of x, y, grad_y, grad_x */
     int32_t param_dtype; /* QkDtype of postact_weights, postact_bias, base_weight, mask */
     uint32_t flags;      /* QkFlags */
-    int32_t reserved;    /* must be 0 */
+    int32_t ansatz;      /* QkAnsatz */
 } QkDesc;
 
 /* ABI version of the loaded library (compare with QK_ABI_VERSION). */

@@ -48,9 +48,20 @@ def use_all_cores() -> int:
     return num_threads()
 
 
-def _flags(preact_trainable: bool, fast_measure: bool, use_postact_bias: bool) -> int:
+ANSATZ_CODES = {"pz_encoding": 0, "pz": 0, "rpz_encoding": 1, "rpz": 1, "real": 2}
+
+
+def _flags(preact_trainable: bool, fast_measure: bool, use_postact_bias: bool, ansatz: str = "pz") -> int:
     return ((PREACT_TRAINABLE if preact_trainable else 0) | (FAST_MEASURE if fast_measure else 0)
-            | (USE_POSTACT_BIAS if use_postact_bias else 0))
+            | (USE_POSTACT_BIAS if use_postact_bias else 0) | (ANSATZ_CODES[ansatz] << 8))
+
+
+def _reps_of(theta: np.ndarray, ansatz: str) -> int:
+    """Repetitions from the theta shape: (O,I,R+1,2) pz, (O,I,R+1,1) rpz, (O,I,R,1) real."""
+    code = ANSATZ_CODES[ansatz]
+    if theta.ndim != 4 or theta.shape[3] != (2 if code == 0 else 1):
+        raise ValueError(f"theta shape {theta.shape} does not fit ansatz {ansatz!r}")
+    return theta.shape[2] - (0 if code == 2 else 1)
 
 
 def _prep(a, dt):
@@ -70,7 +81,7 @@ def _suffix(dtype) -> str:
 
 
 def postacts(x, theta, pw, pb, *, preact_trainable: bool, fast_measure: bool = True,
-             dtype=np.float64) -> np.ndarray:
+             dtype=np.float64, ansatz: str = "pz") -> np.ndarray:
     """Per-edge activations ``(B, O, I)`` — the reference solver contract (solver/_base.py:29-51)."""
     sfx = _suffix(dtype)
     x_, xp = _prep(x, dtype)
@@ -78,12 +89,12 @@ def postacts(x, theta, pw, pb, *, preact_trainable: bool, fast_measure: bool = T
     pw_, pwp = _prep(pw, dtype)
     pb_, pbp = _prep(pb, dtype)
     B, I = x_.shape
-    O, I2, R1, two = th_.shape
-    assert I2 == I and two == 2
-    R = R1 - 1
+    O, I2 = th_.shape[:2]
+    assert I2 == I
+    R = _reps_of(th_, ansatz)
     out = np.empty((B, O, I), dtype=dtype)
     rc = getattr(lib(), f"qkan_oracle_postacts_{sfx}")(
-        B, I, O, R, _flags(preact_trainable, fast_measure, False), xp, thp, pwp, pbp,
+        B, I, O, R, _flags(preact_trainable, fast_measure, False, ansatz), xp, thp, pwp, pbp,
         out.ctypes.data_as(ctypes.c_void_p))
     if rc != 0:
         raise RuntimeError(f"oracle postacts failed ({rc})")
@@ -91,7 +102,8 @@ def postacts(x, theta, pw, pb, *, preact_trainable: bool, fast_measure: bool = T
 
 
 def forward(x, theta, pw, pb, postw, postb=None, basew=None, mask=None, *, preact_trainable: bool,
-            fast_measure: bool = True, use_postact_bias: bool = False, dtype=np.float64) -> np.ndarray:
+            fast_measure: bool = True, use_postact_bias: bool = False, dtype=np.float64,
+            ansatz: str = "pz") -> np.ndarray:
     """Layer output ``y (B, O)`` (qkan.py:750-785)."""
     sfx = _suffix(dtype)
     x_, xp = _prep(x, dtype)
@@ -104,10 +116,10 @@ def forward(x, theta, pw, pb, postw, postb=None, basew=None, mask=None, *, preac
     m_, mp = _prep(mask, dtype)
     B, I = x_.shape
     O = th_.shape[0]
-    R = th_.shape[2] - 1
+    R = _reps_of(th_, ansatz)
     y = np.empty((B, O), dtype=dtype)
     rc = getattr(lib(), f"qkan_oracle_forward_{sfx}")(
-        B, I, O, R, _flags(preact_trainable, fast_measure, use_postact_bias), xp, thp, pwp, pbp, wp,
+        B, I, O, R, _flags(preact_trainable, fast_measure, use_postact_bias, ansatz), xp, thp, pwp, pbp, wp,
         bp, bwp, mp, y.ctypes.data_as(ctypes.c_void_p))
     if rc != 0:
         raise RuntimeError(f"oracle forward failed ({rc})")
@@ -116,7 +128,7 @@ def forward(x, theta, pw, pb, postw, postb=None, basew=None, mask=None, *, preac
 
 def backward(x, theta, pw, pb, postw, postb, basew, mask, gy, *, preact_trainable: bool,
              fast_measure: bool = True, use_postact_bias: bool = False, dtype=np.float64,
-             gpostacts: Optional[np.ndarray] = None) -> dict:
+             gpostacts: Optional[np.ndarray] = None, ansatz: str = "pz") -> dict:
     """All gradients of ``sum(y * gy)``; with ``gpostacts`` the cotangent of the ``(B,O,I)`` tensor instead.
 
     Returns a dict with keys x, theta, preacts_weight, preacts_bias, postact_weights,
@@ -135,10 +147,10 @@ def backward(x, theta, pw, pb, postw, postb, basew, mask, gy, *, preact_trainabl
     gpa_, gpap = _prep(gpostacts, dtype)
     B, I = x_.shape
     O = th_.shape[0]
-    R = th_.shape[2] - 1
+    R = _reps_of(th_, ansatz)
     out = {
         "x": np.zeros((B, I), dtype),
-        "theta": np.zeros((O, I, R + 1, 2), dtype),
+        "theta": np.zeros(th_.shape, dtype),
         "preacts_weight": np.zeros((O, I, R), dtype),
         "preacts_bias": np.zeros((O, I, R), dtype),
         "postact_weights": np.zeros((O, I), dtype),
@@ -147,7 +159,7 @@ def backward(x, theta, pw, pb, postw, postb, basew, mask, gy, *, preact_trainabl
     }
     ptr = {k: v.ctypes.data_as(ctypes.c_void_p) for k, v in out.items()}
     rc = getattr(lib(), f"qkan_oracle_backward_{sfx}")(
-        B, I, O, R, _flags(preact_trainable, fast_measure, use_postact_bias), xp, thp, pwp, pbp, wp,
+        B, I, O, R, _flags(preact_trainable, fast_measure, use_postact_bias, ansatz), xp, thp, pwp, pbp, wp,
         bp, bwp, mp, gyp, gpap, ptr["x"], ptr["theta"], ptr["preacts_weight"], ptr["preacts_bias"],
         ptr["postact_weights"], ptr["postact_bias"], ptr["base_weight"])
     if rc != 0:

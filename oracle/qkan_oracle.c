@@ -7,9 +7,10 @@
  *
  * It restates, gate by gate and with complex amplitudes (NOT the Bloch-vector
  * form the CUDA kernels use), what the reference computes for the
- * "pz_encoding" ansatz:
+ * "pz_encoding", "rpz_encoding" and "real" ansaetze:
  *
- *   circuit      src/qkan/solver/exact.py:90-134   (_pz_encoding)
+ *   circuits     src/qkan/solver/exact.py:90-134 (_pz_encoding), 136-168 (_rpz_encoding), 216-257 (_real)
+ *   X, Z gates   src/qkan/torch_qc.py:337-349
  *   preact enc   src/qkan/solver/exact.py:77-87    (encoded_x = pw*x + pb)
  *   H gate       src/qkan/torch_qc.py:108-121      (h_gate)
  *   Rz gate      src/qkan/torch_qc.py:92-105       (diag(e^{-i phi/2}, e^{+i phi/2}))
@@ -28,7 +29,7 @@
  * Compiled twice: with -DORACLE_F64 (double, symbols *_f64) and without
  * (float, symbols *_f32). Array layouts are the reference's natural-rank,
  * row-major layouts:
- *   x (B,I)  theta (O,I,R+1,2)  preacts_weight/bias (O,I,R)
+ *   x (B,I)  theta (O,I,R+1,2) [rpz: (O,I,R+1,1), real: (O,I,R,1)]  preacts_weight/bias (O,I,R)
  *   postact_weights/postact_bias/base_weight/mask (O,I)  y (B,O)
  */
 #include <math.h>
@@ -146,41 +147,97 @@ static inline real silu_grad(real v) {
     return s * (1 + v * (1 - s));
 }
 
-/* One edge, forward. th = theta[o][i] (R+1,2); pw/pb = preacts[o][i] (R). */
-static inline real edge_forward(real x, const real *th, const real *pw, const real *pb, int R,
-                                unsigned flags, amp_t *states /* 3R+3 or NULL */) {
-    const real h = (real)0.70710678118654752440;
-    amp_t s = {h, 0, h, 0}; /* H|0>  (exact.py:108) */
-    int k = 0;
+/*
+ * Gate lists of the three ansaetze (bits 8-9 of flags: 0 pz, 1 rpz, 2 real).
+ *   pz   exact.py:90-134   per rep Rz(th[l,0]) Ry(th[l,1]) Rz(enc_l); then Rz(th[R,0]) Ry(th[R,1]); theta (R+1,2)
+ *   rpz  exact.py:136-168  per rep Ry(th[l]) Rz(enc_l); then Ry(th[R]); theta (R+1,1); enc always pw*x+pb
+ *   real exact.py:216-257  per rep X Ry(th[l]) Z Ry(enc_l); no final layer; theta (R,1)
+ */
+enum { G_RZ = 0, G_RY = 1, G_X = 2, G_Z = 3 };
+enum { SRC_NONE = -1, SRC_THETA = 0, SRC_ENC = 1 };
+typedef struct {
+    int kind, src, idx;
+} gate_t;
+
+#define QO_ANSATZ(flags) (((flags) >> 8) & 3u)
+#define QO_MAX_GATES (4 * QO_MAX_REPS + 4)
+
+static int theta_per_edge(int ansatz, int R) { return ansatz == 0 ? 2 * (R + 1) : (ansatz == 1 ? R + 1 : R); }
+
+static int build_gates(int ansatz, int R, gate_t *g) {
+    int n = 0;
     for (int l = 0; l < R; ++l) {
-        real enc = (flags & QO_PREACT_TRAINABLE) ? pw[l] * x + pb[l] : x; /* exact.py:87,121-124 */
-        if (states) states[k++] = s;
-        s = apply_rz(s, th[2 * l + 0]);
-        if (states) states[k++] = s;
-        s = apply_ry(s, th[2 * l + 1]);
-        if (states) states[k++] = s;
-        s = apply_rz(s, enc);
+        if (ansatz == 0) {
+            g[n++] = (gate_t){G_RZ, SRC_THETA, 2 * l};
+            g[n++] = (gate_t){G_RY, SRC_THETA, 2 * l + 1};
+            g[n++] = (gate_t){G_RZ, SRC_ENC, l};
+        } else if (ansatz == 1) {
+            g[n++] = (gate_t){G_RY, SRC_THETA, l};
+            g[n++] = (gate_t){G_RZ, SRC_ENC, l};
+        } else {
+            g[n++] = (gate_t){G_X, SRC_NONE, 0};
+            g[n++] = (gate_t){G_RY, SRC_THETA, l};
+            g[n++] = (gate_t){G_Z, SRC_NONE, 0};
+            g[n++] = (gate_t){G_RY, SRC_ENC, l};
+        }
     }
-    if (states) states[k++] = s;
-    s = apply_rz(s, th[2 * R + 0]); /* exact.py:132 */
-    if (states) states[k++] = s;
-    s = apply_ry(s, th[2 * R + 1]); /* exact.py:133 */
-    if (states) states[k++] = s;
+    if (ansatz == 0) {
+        g[n++] = (gate_t){G_RZ, SRC_THETA, 2 * R};
+        g[n++] = (gate_t){G_RY, SRC_THETA, 2 * R + 1};
+    } else if (ansatz == 1) {
+        g[n++] = (gate_t){G_RY, SRC_THETA, R};
+    }
+    return n;
+}
+
+static inline int uses_preacts(unsigned flags) {
+    return (flags & QO_PREACT_TRAINABLE) || QO_ANSATZ(flags) == 1; /* exact.py:75-76 */
+}
+
+static inline real gate_angle(const gate_t *g, real x, const real *th, const real *pw, const real *pb,
+                              unsigned flags) {
+    if (g->src == SRC_THETA) return th[g->idx];
+    return uses_preacts(flags) ? pw[g->idx] * x + pb[g->idx] : x; /* exact.py:87,121-124 */
+}
+
+/* One edge, forward. states (n_gates+1 entries, gate inputs then the final state) may be NULL. */
+static inline real edge_forward(real x, const real *th, const real *pw, const real *pb,
+                                const gate_t *gates, int n_gates, unsigned flags, amp_t *states) {
+    const real h = (real)0.70710678118654752440;
+    amp_t s = {h, 0, h, 0}; /* H|0> */
+    for (int k = 0; k < n_gates; ++k) {
+        const gate_t *g = gates + k;
+        if (states) states[k] = s;
+        if (g->kind == G_RZ) {
+            s = apply_rz(s, gate_angle(g, x, th, pw, pb, flags));
+        } else if (g->kind == G_RY) {
+            s = apply_ry(s, gate_angle(g, x, th, pw, pb, flags));
+        } else if (g->kind == G_X) { /* torch_qc.py:337-343 */
+            amp_t t = {s.a1r, s.a1i, s.a0r, s.a0i};
+            s = t;
+        } else { /* Z, torch_qc.py:345-349 */
+            s.a1r = -s.a1r;
+            s.a1i = -s.a1i;
+        }
+    }
+    if (states) states[n_gates] = s;
     return measure(s, (flags & QO_FAST_MEASURE) != 0);
 }
 
 /* postacts (B,O,I): what the reference solver returns (solver/_base.py contract). */
 int FN(qkan_oracle_postacts)(int B, int I, int O, int R, unsigned flags, const real *x,
                              const real *theta, const real *pw, const real *pb, real *postacts) {
-    if (R < 0 || R > QO_MAX_REPS) return -1;
+    if (R < 0 || R > QO_MAX_REPS || QO_ANSATZ(flags) > 2) return -1;
+    gate_t gates[QO_MAX_GATES];
+    const int ng = build_gates(QO_ANSATZ(flags), R, gates);
+    const int tpe = theta_per_edge(QO_ANSATZ(flags), R);
 #pragma omp parallel for schedule(static)
     for (int b = 0; b < B; ++b)
         for (int o = 0; o < O; ++o)
             for (int i = 0; i < I; ++i) {
                 size_t e = (size_t)o * I + i;
-                postacts[((size_t)b * O + o) * I + i] =
-                    edge_forward(x[(size_t)b * I + i], theta + e * (R + 1) * 2, pw + e * R,
-                                 pb + e * R, R, flags, NULL);
+                postacts[((size_t)b * O + o) * I + i] = edge_forward(
+                    x[(size_t)b * I + i], theta + e * tpe, pw + e * R, pb + e * R, gates, ng, flags, NULL);
             }
     return 0;
 }
@@ -189,8 +246,11 @@ int FN(qkan_oracle_postacts)(int B, int I, int O, int R, unsigned flags, const r
 int FN(qkan_oracle_forward)(int B, int I, int O, int R, unsigned flags, const real *x,
                             const real *theta, const real *pw, const real *pb, const real *postw,
                             const real *postb, const real *basew, const real *mask, real *y) {
-    if (R < 0 || R > QO_MAX_REPS) return -1;
+    if (R < 0 || R > QO_MAX_REPS || QO_ANSATZ(flags) > 2) return -1;
     const int use_pb = (flags & QO_USE_POSTACT_BIAS) && postb;
+    gate_t gates[QO_MAX_GATES];
+    const int ng = build_gates(QO_ANSATZ(flags), R, gates);
+    const int tpe = theta_per_edge(QO_ANSATZ(flags), R);
 #pragma omp parallel for schedule(static)
     for (int b = 0; b < B; ++b)
         for (int o = 0; o < O; ++o) {
@@ -199,8 +259,7 @@ int FN(qkan_oracle_forward)(int B, int I, int O, int R, unsigned flags, const re
                 size_t e = (size_t)o * I + i;
                 real xv = x[(size_t)b * I + i];
                 real m = mask ? mask[e] : 1;
-                real p = edge_forward(xv, theta + e * (R + 1) * 2, pw + e * R, pb + e * R, R,
-                                      flags, NULL);
+                real p = edge_forward(xv, theta + e * tpe, pw + e * R, pb + e * R, gates, ng, flags, NULL);
                 if (use_pb) p += postb[e];
                 acc += p * (postw[e] * m);
                 if (basew) acc += silu(xv) * (basew[e] * m);
@@ -221,12 +280,15 @@ int FN(qkan_oracle_backward)(int B, int I, int O, int R, unsigned flags, const r
                              const real *postb, const real *basew, const real *mask,
                              const real *gy, const real *gpostacts, real *gx, real *gtheta,
                              real *gpw, real *gpb, real *gpostw, real *gpostb, real *gbasew) {
-    if (R < 0 || R > QO_MAX_REPS) return -1;
+    if (R < 0 || R > QO_MAX_REPS || QO_ANSATZ(flags) > 2) return -1;
     const int use_pb = (flags & QO_USE_POSTACT_BIAS) && postb;
     const int fast = (flags & QO_FAST_MEASURE) != 0;
-    const int ptr = (flags & QO_PREACT_TRAINABLE) != 0;
+    const int ptr = uses_preacts(flags);
+    gate_t gates[QO_MAX_GATES];
+    const int ng = build_gates(QO_ANSATZ(flags), R, gates);
+    const int tpe = theta_per_edge(QO_ANSATZ(flags), R);
     size_t nE = (size_t)O * I;
-    if (gtheta) memset(gtheta, 0, nE * (R + 1) * 2 * sizeof(real));
+    if (gtheta) memset(gtheta, 0, nE * tpe * sizeof(real));
     if (gpw) memset(gpw, 0, nE * R * sizeof(real));
     if (gpb) memset(gpb, 0, nE * R * sizeof(real));
     if (gpostw) memset(gpostw, 0, nE * sizeof(real));
@@ -249,18 +311,18 @@ int FN(qkan_oracle_backward)(int B, int I, int O, int R, unsigned flags, const r
         tid = omp_get_thread_num();
 #endif
         real *gxl = gx ? (gx_priv ? gx_priv + (size_t)tid * B * I : gx) : NULL;
-        amp_t states[3 * QO_MAX_REPS + 3];
+        amp_t states[QO_MAX_GATES + 1];
 #pragma omp for schedule(static)
         for (int o = 0; o < O; ++o)
             for (int i = 0; i < I; ++i) {
                 size_t e = (size_t)o * I + i;
-                const real *th = theta + e * (R + 1) * 2;
+                const real *th = theta + e * tpe;
                 const real *pwe = pw + e * R, *pbe = pb + e * R;
                 real m = mask ? mask[e] : 1;
                 real W = gpostacts ? 0 : postw[e] * m;
                 for (int b = 0; b < B; ++b) {
                     real xv = x[(size_t)b * I + i];
-                    real p = edge_forward(xv, th, pwe, pbe, R, flags, states);
+                    real p = edge_forward(xv, th, pwe, pbe, gates, ng, flags, states);
                     real gp;
                     real gxv = 0;
                     if (gpostacts) {
@@ -275,30 +337,33 @@ int FN(qkan_oracle_backward)(int B, int I, int O, int R, unsigned flags, const r
                             gxv += g * basew[e] * m * silu_grad(xv);
                         }
                     }
-                    /* reverse sweep over the 3R+2 gates */
-                    int k = 3 * R + 2;
-                    amp_t bar = measure_vjp(states[k], fast, gp);
-                    real g;
-                    bar = ry_vjp(states[k - 1], th[2 * R + 1], bar, &g);
-                    if (gtheta) gtheta[e * (R + 1) * 2 + 2 * R + 1] += g;
-                    bar = rz_vjp(states[k - 2], th[2 * R + 0], bar, &g);
-                    if (gtheta) gtheta[e * (R + 1) * 2 + 2 * R + 0] += g;
-                    k -= 2;
-                    for (int l = R - 1; l >= 0; --l) {
-                        real enc = ptr ? pwe[l] * xv + pbe[l] : xv;
-                        bar = rz_vjp(states[k - 1], enc, bar, &g);
-                        if (ptr) {
-                            if (gpw) gpw[e * R + l] += g * xv;
-                            if (gpb) gpb[e * R + l] += g;
-                            gxv += g * pwe[l];
+                    /* reverse sweep over the gate list */
+                    amp_t bar = measure_vjp(states[ng], fast, gp);
+                    for (int k = ng - 1; k >= 0; --k) {
+                        const gate_t *gt = gates + k;
+                        real g = 0;
+                        if (gt->kind == G_RZ) {
+                            bar = rz_vjp(states[k], gate_angle(gt, xv, th, pwe, pbe, flags), bar, &g);
+                        } else if (gt->kind == G_RY) {
+                            bar = ry_vjp(states[k], gate_angle(gt, xv, th, pwe, pbe, flags), bar, &g);
+                        } else if (gt->kind == G_X) {
+                            amp_t t = {bar.a1r, bar.a1i, bar.a0r, bar.a0i};
+                            bar = t;
+                            continue;
+                        } else {
+                            bar.a1r = -bar.a1r;
+                            bar.a1i = -bar.a1i;
+                            continue;
+                        }
+                        if (gt->src == SRC_THETA) {
+                            if (gtheta) gtheta[e * tpe + gt->idx] += g;
+                        } else if (ptr) {
+                            if (gpw) gpw[e * R + gt->idx] += g * xv;
+                            if (gpb) gpb[e * R + gt->idx] += g;
+                            gxv += g * pwe[gt->idx];
                         } else {
                             gxv += g;
                         }
-                        bar = ry_vjp(states[k - 2], th[2 * l + 1], bar, &g);
-                        if (gtheta) gtheta[e * (R + 1) * 2 + 2 * l + 1] += g;
-                        bar = rz_vjp(states[k - 3], th[2 * l + 0], bar, &g);
-                        if (gtheta) gtheta[e * (R + 1) * 2 + 2 * l + 0] += g;
-                        k -= 3;
                     }
                     if (gxl) gxl[(size_t)b * I + i] += gxv;
                 }

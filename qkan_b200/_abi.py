@@ -9,14 +9,21 @@ import ctypes
 import os
 from ctypes import POINTER, Structure, c_char_p, c_int, c_int32, c_size_t, c_uint32, c_void_p
 
-QK_ABI_VERSION = 1
+QK_ABI_VERSION = 2
 
 QK_F32 = 0
 QK_BF16 = 1
 
+QK_ANSATZ_PZ = 0
+QK_ANSATZ_RPZ = 1
+QK_ANSATZ_REAL = 2
+ANSATZ_CODES = {"pz_encoding": QK_ANSATZ_PZ, "pz": QK_ANSATZ_PZ, "rpz_encoding": QK_ANSATZ_RPZ,
+                "rpz": QK_ANSATZ_RPZ, "real": QK_ANSATZ_REAL}
+
 QK_PREACT_TRAINABLE = 1
 QK_FAST_MEASURE = 2
 QK_USE_POSTACT_BIAS = 4
+QK_PRECISE_MATH = 8
 
 QK_OK = 0
 QK_ERR_BAD_ARGUMENT = -1
@@ -52,7 +59,7 @@ class QkDesc(Structure):
         ("io_dtype", c_int32),
         ("param_dtype", c_int32),
         ("flags", c_uint32),
-        ("reserved", c_int32),
+        ("ansatz", c_int32),
     ]
 
 
@@ -107,5 +114,5 @@ def desc_pointer(desc: QkDesc):
 
 
 __all__ = [name for name in dir() if name.startswith("QK") or name in (
-    "QkDesc", "QkanLibraryError", "load", "last_error", "check", "desc_pointer", "SYMBOLS", "LIB_PATH")]
+    "QkDesc", "QkanLibraryError", "ANSATZ_CODES", "load", "last_error", "check", "desc_pointer", "SYMBOLS", "LIB_PATH")]
 _ = POINTER  # re-exported for callers that build their own argument blocks

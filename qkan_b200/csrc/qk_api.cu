@@ -25,17 +25,18 @@ int check_desc(const QkDesc* d) {
         return fail(QK_ERR_BAD_ARGUMENT, "negative dimension (B=%d I=%d O=%d)", d->batch, d->in_dim,
                     d->out_dim);
     if (d->reps < 1) return fail(QK_ERR_BAD_ARGUMENT, "reps must be >= 1 (got %d)", d->reps);
-    if (d->reps > qk::kMaxRepsTemplated)
+    if (d->reps > qk::kMaxReps)
         return fail(QK_ERR_UNSUPPORTED, "reps=%d exceeds the compiled maximum of %d", d->reps,
-                    qk::kMaxRepsTemplated);
+                    qk::kMaxReps);
+    if (d->ansatz != QK_ANSATZ_PZ && d->ansatz != QK_ANSATZ_RPZ && d->ansatz != QK_ANSATZ_REAL)
+        return fail(QK_ERR_BAD_ARGUMENT, "ansatz %d is not a QkAnsatz value", d->ansatz);
     if (d->io_dtype != QK_F32 && d->io_dtype != QK_BF16)
         return fail(QK_ERR_BAD_ARGUMENT, "io_dtype %d is neither QK_F32 nor QK_BF16", d->io_dtype);
     if (d->param_dtype != QK_F32 && d->param_dtype != QK_BF16)
         return fail(QK_ERR_BAD_ARGUMENT, "param_dtype %d is neither QK_F32 nor QK_BF16",
                     d->param_dtype);
-    if (d->flags & ~(QK_PREACT_TRAINABLE | QK_FAST_MEASURE | QK_USE_POSTACT_BIAS))
+    if (d->flags & ~(QK_PREACT_TRAINABLE | QK_FAST_MEASURE | QK_USE_POSTACT_BIAS | QK_PRECISE_MATH))
         return fail(QK_ERR_BAD_ARGUMENT, "unknown flag bits 0x%x", d->flags);
-    if (d->reserved != 0) return fail(QK_ERR_BAD_ARGUMENT, "reserved field must be 0");
     if ((long long)d->out_dim > 65535)
         return fail(QK_ERR_UNSUPPORTED, "out_dim %d exceeds 65535", d->out_dim);
     return QK_OK;
@@ -51,7 +52,7 @@ Layout forward_layout(const QkDesc& d) {
     Layout l{};
     l.ipad = qk::round_up(d.in_dim, 32);
     l.table_off = 0;
-    size_t table = (size_t)d.out_dim * qk::table_rows(d.reps) * l.ipad * sizeof(float);
+    size_t table = (size_t)d.out_dim * qk::table_rows(qk::compiled_reps(d.ansatz, d.reps)) * l.ipad * sizeof(float);
     l.bias_off = qk::align256(table);
     l.total = l.bias_off + qk::align256((size_t)d.out_dim * sizeof(float));
     return l;
@@ -106,6 +107,8 @@ int run_forward(const QkDesc* desc, const void* x, const float* theta, const flo
     p.in_dim = d.in_dim;
     p.out_dim = d.out_dim;
     p.reps = d.reps;
+    p.rk = qk::compiled_reps(d.ansatz, d.reps);
+    p.ansatz = d.ansatz;
     p.ipad = l.ipad;
     p.flags = d.flags;
     p.param_dtype = d.param_dtype;
@@ -126,6 +129,7 @@ int run_forward(const QkDesc* desc, const void* x, const float* theta, const flo
     f.in_dim = d.in_dim;
     f.out_dim = d.out_dim;
     f.ipad = l.ipad;
+    f.precise = (d.flags & QK_PRECISE_MATH) != 0;
     f.cfg = qk::choose_fwd_cfg(d, edges, has_base);
     if (getenv("QK_DEBUG"))
         fprintf(stderr, "[qk] forward B=%d I=%d O=%d R=%d: tile %d rows x %d outputs, grid %d x %d, smem %zu\n",
@@ -135,7 +139,7 @@ int run_forward(const QkDesc* desc, const void* x, const float* theta, const flo
     f.bias = p.bias;
     f.y = y;
     f.postacts = postacts;
-    e = qk::launch_forward(f, d.reps, (d.flags & QK_FAST_MEASURE) != 0, d.io_dtype, has_base, st);
+    e = qk::launch_forward(f, p.rk, (d.flags & QK_FAST_MEASURE) != 0, d.io_dtype, has_base, st);
     if (e != cudaSuccess) return cuda_fail(e, "forward launch");
     return QK_OK;
 }
@@ -155,7 +159,9 @@ int run_backward(const QkDesc* desc, const void* x, const float* theta, const fl
         cudaError_t e = cudaSuccess;
         size_t es = d.io_dtype == QK_BF16 ? 2 : 4;
         if (gx && (size_t)d.batch * d.in_dim) e = cudaMemsetAsync(gx, 0, (size_t)d.batch * d.in_dim * es, st);
-        if (e == cudaSuccess && gtheta && nE) e = cudaMemsetAsync(gtheta, 0, nE * (d.reps + 1) * 2 * 4, st);
+        const size_t theta_per_edge = d.ansatz == QK_ANSATZ_PZ ? (size_t)(d.reps + 1) * 2
+                                      : (d.ansatz == QK_ANSATZ_RPZ ? (size_t)d.reps + 1 : (size_t)d.reps);
+        if (e == cudaSuccess && gtheta && nE) e = cudaMemsetAsync(gtheta, 0, nE * theta_per_edge * 4, st);
         if (e == cudaSuccess && gpw && nE) e = cudaMemsetAsync(gpw, 0, nE * d.reps * 4, st);
         if (e == cudaSuccess && gpb && nE) e = cudaMemsetAsync(gpb, 0, nE * d.reps * 4, st);
         if (e == cudaSuccess && gpostw && nE) e = cudaMemsetAsync(gpostw, 0, nE * 4, st);
@@ -178,6 +184,8 @@ int run_backward(const QkDesc* desc, const void* x, const float* theta, const fl
     p.in_dim = d.in_dim;
     p.out_dim = d.out_dim;
     p.reps = d.reps;
+    p.rk = qk::compiled_reps(d.ansatz, d.reps);
+    p.ansatz = d.ansatz;
     p.ipad = l.ipad;
     p.flags = d.flags;
     p.param_dtype = d.param_dtype;
@@ -206,6 +214,7 @@ int run_backward(const QkDesc* desc, const void* x, const float* theta, const fl
     b.in_dim = d.in_dim;
     b.out_dim = d.out_dim;
     b.ipad = l.ipad;
+    b.precise = (d.flags & QK_PRECISE_MATH) != 0;
     b.cfg = qk::choose_bwd_cfg(d, has_base);
     if (getenv("QK_DEBUG"))
         fprintf(stderr, "[qk] backward B=%d I=%d O=%d R=%d: %d groups x %d rows, grid %d x %d, smem %zu, ru %d\n",
@@ -217,7 +226,7 @@ int run_backward(const QkDesc* desc, const void* x, const float* theta, const fl
     b.table = p.table;
     b.gx = gx;
     b.partials = reinterpret_cast<float*>(wsb + l.partials_off);
-    e = qk::launch_backward(b, d.reps, (d.flags & QK_FAST_MEASURE) != 0, d.io_dtype, has_base, st);
+    e = qk::launch_backward(b, p.rk, (d.flags & QK_FAST_MEASURE) != 0, d.io_dtype, has_base, st);
     if (e != cudaSuccess) return cuda_fail(e, "backward launch");
 
     if (gtheta || gpw || gpb || gpostw || gpostb || gbasew) {
@@ -225,6 +234,8 @@ int run_backward(const QkDesc* desc, const void* x, const float* theta, const fl
         f.in_dim = d.in_dim;
         f.out_dim = d.out_dim;
         f.reps = d.reps;
+        f.rk = p.rk;
+        f.ansatz = d.ansatz;
         f.ipad = l.ipad;
         f.nacc = b.cfg.nacc;
         f.ntiles = b.cfg.grid_b;

@@ -15,17 +15,41 @@
 // reduction) and written as this batch tile's partial; finish_grads then sums
 // the tiles in a fixed order (cross-CTA reduction, bitwise reproducible).
 #pragma once
+#include <type_traits>
+
 #include "qk_kernels.cuh"
 
 namespace qk {
 
 __device__ __forceinline__ float sigmoid_f(float v) { return 1.f / (1.f + expf(-v)); }
 
-template <int R, bool FAST, bool BASE, bool EDGES, int NACC>
+template <int R, bool FAST, bool BASE, bool EDGES, int NACC, bool PRECISE>
 __device__ __forceinline__ float edge_backward(const EdgeFwd<R>& e, float bw, float x, float g,
                                                float sl, float dsl, float (&acc)[NACC]) {
+    if constexpr (R == 0) {
+        // "real" ansatz: p = f(alpha), alpha = A x + C. acc[0] = sum dL/dalpha, acc[1] = sum dL/dalpha * x
+        float s, c, r = 1.f;
+        const float p = real_forward<FAST, PRECISE>(e, x, s, c, r);
+        const float gp = EDGES ? g : g * e.w;
+        if (!EDGES) acc[a_w(0)] = fmaf(g, p, acc[a_w(0)]);
+        float dp = -s;
+        if (FAST) {
+            // d/dalpha [cos * (1+|sin|)^(-1/2)] = -sin r - (1/2) cos^2 r^3 sign(sin)
+            const float sgn = s > 0.f ? 1.f : (s < 0.f ? -1.f : 0.f);
+            dp = -fmaf((0.5f * c) * c, (r * r) * (r * sgn), s * r);
+        }
+        const float ga = gp * dp;
+        acc[0] += ga;
+        acc[1] = fmaf(ga, x, acc[1]);
+        float gx = ga * e.a;
+        if (BASE) {
+            acc[a_bw(0)] = fmaf(g, sl, acc[a_bw(0)]);
+            gx = fmaf(g * bw, dsl, gx);
+        }
+        return gx;
+    } else {
     float cs[R], sn[R], vx, vy, vz, inv_rho, r;
-    const float p = edge_forward<R, FAST, true>(e, x, cs, sn, vx, vy, vz, inv_rho, r);
+    const float p = edge_forward<R, FAST, true, PRECISE>(e, x, cs, sn, vx, vy, vz, inv_rho, r);
     const float gp = EDGES ? g : g * e.w;
     if (!EDGES) acc[a_w(R)] = fmaf(g, p, acc[a_w(R)]);
     // w = v x a, a = cotangent of the final Bloch vector (its z component of w is 0)
@@ -71,12 +95,13 @@ __device__ __forceinline__ float edge_backward(const EdgeFwd<R>& e, float bw, fl
         gx = fmaf(g * bw, dsl, gx);
     }
     return gx;
+    }
 }
 
 constexpr int kGyChunk = 8;  // outputs whose grad_y columns are staged together
 
-template <int R, bool FAST, typename IO, bool BASE, bool EDGES, int RU>
-__global__ void __launch_bounds__(512) backward_kernel(BwdArgs a) {
+template <int R, bool FAST, typename IO, bool BASE, bool EDGES, int RU, bool PRECISE>
+__global__ void __launch_bounds__(256) backward_kernel(BwdArgs a) {
     constexpr int NACC = acc_rows(R, BASE);
     // floats per tile row: 32 (x, grad_x) pairs [+ 32 (silu, silu') pairs]; a pair is one 64-bit access
     constexpr int ROW = BASE ? 128 : 64;
@@ -173,7 +198,7 @@ __global__ void __launch_bounds__(512) backward_kernel(BwdArgs a) {
                 }
 #pragma unroll
                 for (int u = 0; u < RU; ++u) {
-                    float gx = edge_backward<R, FAST, BASE, EDGES, NACC>(e, bw, xv[u], g[u], sl[u],
+                    float gx = edge_backward<R, FAST, BASE, EDGES, NACC, PRECISE>(e, bw, xv[u], g[u], sl[u],
                                                                          dsl[u], acc);
                     p[u * ROW + 1] = gxo[u] + gx;
                 }
@@ -205,8 +230,11 @@ __global__ void __launch_bounds__(512) backward_kernel(BwdArgs a) {
 
 template <int R, bool FAST, typename IO, bool BASE, bool EDGES>
 static cudaError_t launch_bwd_t(const BwdArgs& a, cudaStream_t st) {
-    auto kern = a.cfg.ru == 4 ? backward_kernel<R, FAST, IO, BASE, EDGES, 4>
-                              : backward_kernel<R, FAST, IO, BASE, EDGES, 2>;
+    auto kern = a.cfg.ru == 4 ? backward_kernel<R, FAST, IO, BASE, EDGES, 4, false>
+                              : backward_kernel<R, FAST, IO, BASE, EDGES, 2, false>;
+    if constexpr (std::is_same<IO, float>::value) {  // the full-precision variant exists for float32 I/O
+        if (a.precise) kern = backward_kernel<R, FAST, IO, BASE, EDGES, 2, true>;
+    }
     cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            (int)a.cfg.smem);
     if (err != cudaSuccess) return err;

@@ -30,7 +30,15 @@
 namespace qk {
 
 constexpr int kWarp = 32;
-constexpr int kMaxRepsTemplated = 8;
+constexpr int kMaxReps = 16;
+
+// The kernels are instantiated for these repetition counts. A circuit with more than 8
+// repetitions runs in the next larger instantiation, padded with identity gates (zero
+// angles, zero preact weight). 0 is the instantiation of the "real" ansatz, whose whole
+// circuit collapses to one data-dependent angle (see EdgeFwd<0>).
+__host__ __device__ constexpr int compiled_reps(int ansatz, int reps) {
+    return ansatz == QK_ANSATZ_REAL ? 0 : (reps <= 8 ? reps : (reps <= 12 ? 12 : 16));
+}
 
 // ---- per-edge constant table -------------------------------------------------
 // table[(o * K + k) * ipad + i], float32, ipad = in_dim rounded up to 32.
@@ -98,23 +106,59 @@ __device__ __forceinline__ float ld_param(const void* p, int dtype, size_t idx) 
 // sin/cos of the data angle on the special-function unit. The angles are
 // pw*x + c with |c| <= ~2*pi and moderate |pw*x|; the unit's absolute error is
 // ~4e-7 there, well inside the 1e-5 normalised tolerance of the layer outputs.
-__device__ __forceinline__ void fast_sincos(float a, float& s, float& c) {
-#ifdef QK_PRECISE_TRIG
-    sincosf(a, &s, &c);
-#else
-    asm("sin.approx.ftz.f32 %0, %1;" : "=f"(s) : "f"(a));
-    asm("cos.approx.ftz.f32 %0, %1;" : "=f"(c) : "f"(a));
-#endif
+// PRECISE selects the full-precision library routines instead: their error is ~1 ulp and varies
+// smoothly with the argument, which quasi-Newton optimisers (LBFGS on small fits) rely on when they
+// difference gradients; the SFU path is ~4x faster per call and is the default for large layers.
+// sin and cos to ~1 ulp on the FMA pipe: three-term Cody-Waite reduction by pi/2 (exact products for
+// |a| < ~1e4, graceful beyond) and the classic degree-7 / degree-8 minimax polynomials on [-pi/4, pi/4].
+// Kept branch-free and small so that the full-precision kernel variants stay compact.
+__device__ __forceinline__ void precise_sincos(float a, float& s, float& c) {
+    const float j = rintf(a * 0.63661977236758134f);
+    float r = fmaf(j, -1.5703125f, a);
+    r = fmaf(j, -4.837512969970703125e-4f, r);
+    r = fmaf(j, -7.54978995489188216e-8f, r);
+    const float z = r * r;
+    float ps = fmaf(z, -1.9515295891e-4f, 8.3321608736e-3f);
+    ps = fmaf(ps, z, -1.6666654611e-1f);
+    ps = fmaf(ps * z, r, r);  // sin(r)
+    float pc = fmaf(z, 2.443315711809948e-5f, -1.388731625493765e-3f);
+    pc = fmaf(pc, z, 4.166664568298827e-2f);
+    pc = fmaf(pc * z, z, fmaf(z, -0.5f, 1.0f));  // cos(r)
+    const int q = (int)j;
+    const float ss = (q & 1) ? pc : ps;
+    const float cc = (q & 1) ? ps : pc;
+    s = (q & 2) ? -ss : ss;
+    c = ((q + 1) & 2) ? -cc : cc;
 }
-__device__ __forceinline__ float fast_rsqrt(float a) {
-    float r;
-    asm("rsqrt.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(a));
-    return r;
+
+template <bool PRECISE>
+__device__ __forceinline__ void qk_sincos(float a, float& s, float& c) {
+    if constexpr (PRECISE) {
+        precise_sincos(a, s, c);
+    } else {
+        asm("sin.approx.ftz.f32 %0, %1;" : "=f"(s) : "f"(a));
+        asm("cos.approx.ftz.f32 %0, %1;" : "=f"(c) : "f"(a));
+    }
 }
-__device__ __forceinline__ float fast_sqrt(float a) {
-    float r;
-    asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(a));
-    return r;
+template <bool PRECISE>
+__device__ __forceinline__ float qk_rsqrt(float a) {
+    if constexpr (PRECISE) {
+        return 1.0f / sqrtf(a);
+    } else {
+        float r;
+        asm("rsqrt.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(a));
+        return r;
+    }
+}
+template <bool PRECISE>
+__device__ __forceinline__ float qk_sqrt(float a) {
+    if constexpr (PRECISE) {
+        return sqrtf(a);
+    } else {
+        float r;
+        asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(a));
+        return r;
+    }
 }
 
 // ---- per-edge constants in registers -----------------------------------------
@@ -149,12 +193,39 @@ struct EdgeFwd {
     }
 };
 
+// "real" ansatz (reference: src/qkan/solver/exact.py:216-257): every gate is an Ry or a reflection
+// in the x-z plane, so the circuit is one rotation by alpha = A x + C with A = sum_l pw_l (or reps)
+// and C = pi/2 + sum_l (pb_l - theta_l - pi); readout cos(alpha) (Born) or
+// cos(alpha) rsqrt(1 + |sin(alpha)|) (fast). Table rows: 0 = A, 1 = C reduced to [-pi,pi], 3 = weight.
+template <>
+struct EdgeFwd<0> {
+    float a, c, w;
+    __device__ __forceinline__ void load(const float* __restrict__ t, int stride) {
+        a = t[0];
+        c = t[stride];
+        w = t[t_w(0) * stride];
+    }
+    __device__ __forceinline__ void load_bwd_extra(const float*, int) {}
+};
+
+template <bool FAST, bool PRECISE>
+__device__ __forceinline__ float real_forward(const EdgeFwd<0>& e, float x, float& s, float& c, float& r) {
+    qk_sincos<PRECISE>(fmaf(e.a, x, e.c), s, c);
+    if (!FAST) return c;
+    r = qk_rsqrt<PRECISE>(1.0f + fabsf(s));
+    return c * r;
+}
+
 // Forward of one edge for one batch row: returns the readout p (before bias and weight).
 // When KEEP is true the data-gate sin/cos and the final Bloch vector are returned for the backward.
-template <int R, bool FAST, bool KEEP>
+template <int R, bool FAST, bool KEEP, bool PRECISE>
 __device__ __forceinline__ float edge_forward(const EdgeFwd<R>& e, float x, float* cs, float* sn,
                                               float& vx, float& vy, float& vz, float& inv_rho,
                                               float& r) {
+    if constexpr (R == 0) {
+        float s, c;
+        return real_forward<FAST, PRECISE>(e, x, s, c, r);
+    } else {
     vx = e.vx0;
     vy = e.vy0;
     vz = e.vz0;
@@ -167,7 +238,7 @@ __device__ __forceinline__ float edge_forward(const EdgeFwd<R>& e, float x, floa
             vz = nz;
         }
         float s, c;
-        fast_sincos(fmaf(e.pw[l], x, e.c[l]), s, c);  // merged Rz(pw_l x + pb_l + theta[l+1,0])
+        qk_sincos<PRECISE>(fmaf(e.pw[l], x, e.c[l]), s, c);  // merged Rz(pw_l x + pb_l + theta[l+1,0])
         if (KEEP) {
             cs[l] = c;
             sn[l] = s;
@@ -186,12 +257,13 @@ __device__ __forceinline__ float edge_forward(const EdgeFwd<R>& e, float x, floa
     if (!FAST) return vz;
     float s2 = fmaf(vx, vx, vy * vy);
     if (KEEP) {
-        inv_rho = fast_rsqrt(fmaxf(s2, 1e-30f));
-        r = fast_rsqrt(fmaf(s2, inv_rho, 1.0f));
+        inv_rho = qk_rsqrt<PRECISE>(fmaxf(s2, 1e-30f));
+        r = qk_rsqrt<PRECISE>(fmaf(s2, inv_rho, 1.0f));
     } else {
-        r = fast_rsqrt(1.0f + fast_sqrt(s2));
+        r = qk_rsqrt<PRECISE>(1.0f + qk_sqrt<PRECISE>(s2));
     }
     return vz * r;
+    }
 }
 
 }  // namespace qk

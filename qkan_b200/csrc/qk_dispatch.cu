@@ -23,7 +23,7 @@ cudaError_t launch_bwd_d(const BwdArgs& a, bool fast, int io_dtype, bool has_bas
 #define QK_DECL(R)                                                                              \
     extern template cudaError_t launch_fwd_d<R>(const FwdArgs&, bool, int, bool, cudaStream_t); \
     extern template cudaError_t launch_bwd_d<R>(const BwdArgs&, bool, int, bool, cudaStream_t);
-QK_DECL(1) QK_DECL(2) QK_DECL(3) QK_DECL(4) QK_DECL(5) QK_DECL(6) QK_DECL(7) QK_DECL(8)
+QK_DECL(0) QK_DECL(1) QK_DECL(2) QK_DECL(3) QK_DECL(4) QK_DECL(5) QK_DECL(6) QK_DECL(7) QK_DECL(8) QK_DECL(12) QK_DECL(16)
 #undef QK_DECL
 
 constexpr int kSmCount = 148;
@@ -65,9 +65,10 @@ FwdCfg choose_fwd_cfg(const QkDesc& d, bool edges, bool base) {
 }
 
 BwdCfg choose_bwd_cfg(const QkDesc& d, bool base) {
-    const int nacc = acc_rows(d.reps, base);
+    const int rk = compiled_reps(d.ansatz, d.reps);
+    const int nacc = acc_rows(rk, base);
     const int grid_i = (d.in_dim + 31) / 32;
-    const int ru = tune_int("QK_BWD_RU", 4);
+    const int ru = tune_int("QK_BWD_RU", rk > 8 ? 2 : 4);  // long circuits: fewer rows in flight, no spills
     auto make = [&](int groups, int rpg) {
         const int tb = groups * rpg;
         size_t smem = (size_t)tb * 32 * 4 * (base ? 4 : 2) + (size_t)kGyChunkHost * tb * 4 +
@@ -78,10 +79,10 @@ BwdCfg choose_bwd_cfg(const QkDesc& d, bool base) {
     if (force_groups > 0 && force_rpg > 0) return make(force_groups, force_rpg);  // developer override
     // (row groups = warps per CTA, rows per group), largest tile first
     static const int cand[][2] = {{8, 32}, {8, 16}, {4, 32}, {4, 16}, {8, 8}, {2, 32}, {4, 8}, {2, 16}, {2, 8}, {1, 8}};
-    const int regs_est = 34 + 11 * d.reps > 255 ? 255 : 34 + 11 * d.reps;
+    const int regs_est = rk > 8 ? 255 : 34 + 11 * rk;
     const int ipad = round_up(d.in_dim, 32);
     // seconds per (row x 32 columns x output) on one SM: ~(28 R + 20) instructions at 0.72 IPC x 4 schedulers
-    const double t_unit = (28.0 * d.reps + 20.0) / (4 * 0.72 * 1.965e9);
+    const double t_unit = (28.0 * rk + 20.0) / (4 * 0.72 * 1.965e9);
     const double partial_cap = 8.0 * 1024 * 1024 * 1024;  // bytes of per-tile partials we are willing to hold
     BwdCfg best{};
     double best_cost = -1.0;
@@ -126,6 +127,9 @@ cudaError_t launch_forward(const FwdArgs& a, int reps, bool fast, int io_dtype, 
         case 6: return launch_fwd_d<6>(a, fast, io_dtype, has_base, st);
         case 7: return launch_fwd_d<7>(a, fast, io_dtype, has_base, st);
         case 8: return launch_fwd_d<8>(a, fast, io_dtype, has_base, st);
+        case 12: return launch_fwd_d<12>(a, fast, io_dtype, has_base, st);
+        case 16: return launch_fwd_d<16>(a, fast, io_dtype, has_base, st);
+        case 0: return launch_fwd_d<0>(a, fast, io_dtype, has_base, st);
         default: return cudaErrorInvalidValue;
     }
 }
@@ -141,6 +145,9 @@ cudaError_t launch_backward(const BwdArgs& a, int reps, bool fast, int io_dtype,
         case 6: return launch_bwd_d<6>(a, fast, io_dtype, has_base, st);
         case 7: return launch_bwd_d<7>(a, fast, io_dtype, has_base, st);
         case 8: return launch_bwd_d<8>(a, fast, io_dtype, has_base, st);
+        case 12: return launch_bwd_d<12>(a, fast, io_dtype, has_base, st);
+        case 16: return launch_bwd_d<16>(a, fast, io_dtype, has_base, st);
+        case 0: return launch_bwd_d<0>(a, fast, io_dtype, has_base, st);
         default: return cudaErrorInvalidValue;
     }
 }

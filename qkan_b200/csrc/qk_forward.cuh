@@ -9,6 +9,8 @@
 // the x tile is staged once in shared memory with coalesced loads, and the sum
 // over in_dim is a warp-shuffle transpose-reduction done once per 32 rows.
 #pragma once
+#include <type_traits>
+
 #include "qk_kernels.cuh"
 
 namespace qk {
@@ -31,7 +33,7 @@ __device__ __forceinline__ float transpose_reduce32(float (&v)[32], int lane) {
 
 __device__ __forceinline__ float silu_f(float v) { return v / (1.f + expf(-v)); }
 
-template <int R, bool FAST, typename IO, bool BASE, bool EDGES>
+template <int R, bool FAST, typename IO, bool BASE, bool EDGES, bool PRECISE>
 __global__ void __launch_bounds__(512) forward_kernel(FwdArgs a) {
     extern __shared__ __align__(16) float smem[];
     const int tb = a.cfg.tb, ot = a.cfg.ot, ich = a.cfg.ich;
@@ -79,7 +81,7 @@ __global__ void __launch_bounds__(512) forward_kernel(FwdArgs a) {
                     for (int r = 0; r < 32; ++r) {
                         float xv = x_s[(rg + r) * ich + col];
                         float vx, vy, vz, ir, rr;
-                        float p = edge_forward<R, FAST, false>(e, xv, nullptr, nullptr, vx, vy, vz,
+                        float p = edge_forward<R, FAST, false, PRECISE>(e, xv, nullptr, nullptr, vx, vy, vz,
                                                                ir, rr);
                         if (EDGES) {
                             v[r] = p;
@@ -119,7 +121,10 @@ __global__ void __launch_bounds__(512) forward_kernel(FwdArgs a) {
 
 template <int R, bool FAST, typename IO, bool BASE, bool EDGES>
 static cudaError_t launch_fwd_t(const FwdArgs& a, cudaStream_t st) {
-    auto kern = forward_kernel<R, FAST, IO, BASE, EDGES>;
+    auto kern = forward_kernel<R, FAST, IO, BASE, EDGES, false>;
+    if constexpr (std::is_same<IO, float>::value) {  // the full-precision variant exists for float32 I/O
+        if (a.precise) kern = forward_kernel<R, FAST, IO, BASE, EDGES, true>;
+    }
     cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            (int)a.cfg.smem);
     if (err != cudaSuccess) return err;

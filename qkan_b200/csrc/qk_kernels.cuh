@@ -7,6 +7,8 @@ namespace qk {
 
 struct PrepArgs {
     int in_dim, out_dim, reps, ipad;
+    int rk;      // compiled_reps(ansatz, reps): the table is laid out for this repetition count
+    int ansatz;  // QkAnsatz
     unsigned flags;
     int param_dtype;
     const float* theta;
@@ -22,6 +24,7 @@ struct PrepArgs {
 
 struct FinishArgs {
     int in_dim, out_dim, reps, ipad, nacc, ntiles, ncolsplit, has_base;
+    int rk, ansatz;
     unsigned flags;
     int param_dtype;
     const float* partials;
@@ -57,6 +60,7 @@ struct BwdCfg {
 
 struct FwdArgs {
     int batch, in_dim, out_dim, ipad;
+    int precise;  // QK_PRECISE_MATH requested (honoured for float32 I/O)
     FwdCfg cfg;
     const void* x;
     const float* table;
@@ -67,6 +71,7 @@ struct FwdArgs {
 
 struct BwdArgs {
     int batch, in_dim, out_dim, ipad;
+    int precise;  // QK_PRECISE_MATH requested (honoured for float32 I/O)
     BwdCfg cfg;
     const void* x;
     const void* gy;         // (B,O) fused mode

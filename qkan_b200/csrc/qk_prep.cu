@@ -12,45 +12,73 @@ __global__ void prep_table_kernel(PrepArgs a) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     const int o = blockIdx.y;
     if (i >= a.ipad) return;
-    const int R = a.reps;
-    const int K = table_rows(R);
+    const int R = a.reps, RK = a.rk;
+    const int K = table_rows(RK);
     float* t = a.table + (size_t)o * K * a.ipad + i;
+    auto put = [&](int row, float v) { t[(size_t)row * a.ipad] = v; };
     if (i >= a.in_dim) {
-        for (int k = 0; k < K; ++k) t[(size_t)k * a.ipad] = 0.f;
+        for (int k = 0; k < K; ++k) put(k, 0.f);
         return;
     }
     const size_t e = (size_t)o * a.in_dim + i;
-    const float* th = a.theta + e * (R + 1) * 2;
-    const bool ptr = (a.flags & QK_PREACT_TRAINABLE) != 0;
+    const float m = a.mask ? ld_param(a.mask, a.param_dtype, e) : 1.f;
+    const float w = a.postw ? ld_param(a.postw, a.param_dtype, e) * m : 1.f;
+    const float bw = a.basew ? ld_param(a.basew, a.param_dtype, e) * m : 0.f;
+    // rpz always encodes pw*x + pb (src/qkan/solver/exact.py:75-76)
+    const bool ptr = (a.flags & QK_PREACT_TRAINABLE) != 0 || a.ansatz == QK_ANSATZ_RPZ;
+
+    if (a.ansatz == QK_ANSATZ_REAL) {
+        // alpha = A x + C; C is reduced to [-pi, pi] in double so the SFU sees a small argument
+        const float* th = a.theta + e * R;
+        double A = 0.0, C = 1.5707963267948966;
+        for (int l = 0; l < R; ++l) {
+            A += ptr ? (double)a.pw[e * R + l] : 1.0;
+            C += (ptr ? (double)a.pb[e * R + l] : 0.0) - (double)th[l] - 3.141592653589793;
+        }
+        C -= 6.283185307179586 * rint(C / 6.283185307179586);
+        for (int k = 0; k < K; ++k) put(k, 0.f);
+        put(0, (float)A);
+        put(1, (float)C);
+        put(t_w(0), w);
+        put(t_bw(0), bw);
+        return;
+    }
+
+    const bool pz = a.ansatz == QK_ANSATZ_PZ;
+    const int ts = pz ? 2 : 1;  // floats of theta per layer
+    const float* th = a.theta + e * (R + 1) * ts;
+    auto th_ry = [&](int l) { return pz ? th[2 * l + 1] : th[l]; };   // Ry angle of layer l
+    auto th_rz = [&](int l) { return pz ? th[2 * l] : 0.f; };          // Rz angle of layer l (pz only)
     float s00, c00, sa0, ca0;
-    sincosf(th[0], &s00, &c00);
-    sincosf(th[1], &sa0, &ca0);
-    // start vector: Ry(theta[0,1]) Rz(theta[0,0]) applied to (1,0,0)
-    t[(size_t)t_vx0() * a.ipad] = c00 * ca0;
-    t[(size_t)t_vy0() * a.ipad] = s00;
-    t[(size_t)t_vz0() * a.ipad] = -c00 * sa0;
-    t[(size_t)t_ca0(R) * a.ipad] = ca0;
-    t[(size_t)t_sa0(R) * a.ipad] = sa0;
-    for (int l = 0; l < R; ++l) {
-        float w = ptr ? a.pw[e * R + l] : 1.f;
-        float b = ptr ? a.pb[e * R + l] : 0.f;
-        t[(size_t)t_pw(l) * a.ipad] = w;
-        t[(size_t)t_c(l) * a.ipad] = b + th[2 * (l + 1)];
+    sincosf(th_rz(0), &s00, &c00);
+    sincosf(th_ry(0), &sa0, &ca0);
+    // start vector: Ry(theta_ry[0]) Rz(theta_rz[0]) applied to (1,0,0)
+    put(t_vx0(), c00 * ca0);
+    put(t_vy0(), s00);
+    put(t_vz0(), -c00 * sa0);
+    put(t_ca0(RK), ca0);
+    put(t_sa0(RK), sa0);
+    for (int l = 0; l < RK; ++l) {
+        if (l < R) {
+            put(t_pw(l), ptr ? a.pw[e * R + l] : 1.f);
+            put(t_c(l), (ptr ? a.pb[e * R + l] : 0.f) + th_rz(l + 1));
+        } else {  // identity padding
+            put(t_pw(l), 0.f);
+            put(t_c(l), 0.f);
+        }
         if (l >= 1) {
-            float s, c;
-            sincosf(th[2 * l + 1], &s, &c);
-            t[(size_t)t_ca(R, l) * a.ipad] = c;
-            t[(size_t)t_sa(R, l) * a.ipad] = s;
+            float s = 0.f, c = 1.f;
+            if (l < R) sincosf(th_ry(l), &s, &c);
+            put(t_ca(RK, l), c);
+            put(t_sa(RK, l), s);
         }
     }
     float sf, cf;
-    sincosf(th[2 * R + 1], &sf, &cf);
-    t[(size_t)t_cf(R) * a.ipad] = cf;
-    t[(size_t)t_sf(R) * a.ipad] = sf;
-    float m = a.mask ? ld_param(a.mask, a.param_dtype, e) : 1.f;
-    float w = a.postw ? ld_param(a.postw, a.param_dtype, e) * m : 1.f;
-    t[(size_t)t_w(R) * a.ipad] = w;
-    t[(size_t)t_bw(R) * a.ipad] = a.basew ? ld_param(a.basew, a.param_dtype, e) * m : 0.f;
+    sincosf(th_ry(R), &sf, &cf);
+    put(t_cf(RK), cf);
+    put(t_sf(RK), sf);
+    put(t_w(RK), w);
+    put(t_bw(RK), bw);
 }
 
 // one warp per output: fixed lane-strided order + shuffle tree => deterministic
@@ -99,10 +127,10 @@ __global__ void finish_grads_kernel(FinishArgs a) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     const int o = blockIdx.y;
     if (i >= a.in_dim) return;
-    const int R = a.reps;
+    const int R = a.reps, RK = a.rk;
     const int nacc = a.nacc;
     const size_t e = (size_t)o * a.in_dim + i;
-    const bool ptr = (a.flags & QK_PREACT_TRAINABLE) != 0;
+    const bool ptr = (a.flags & QK_PREACT_TRAINABLE) != 0 || a.ansatz == QK_ANSATZ_RPZ;
     const bool use_pb = (a.flags & QK_USE_POSTACT_BIAS) != 0 && a.postb != nullptr;
     const size_t tile_stride = (size_t)a.out_dim * nacc * a.ipad;
     const float* p0 = a.partials + ((size_t)o * nacc) * a.ipad + i;
@@ -112,16 +140,38 @@ __global__ void finish_grads_kernel(FinishArgs a) {
         for (int t = 0; t < a.ntiles; ++t) s += p[(size_t)t * tile_stride];
         return s;
     };
-    if (a.gtheta) {
-        float* g = a.gtheta + e * (R + 1) * 2;
-        g[0] = total(a_t00(R));
-        for (int l = 0; l <= R; ++l) g[2 * l + 1] = total(a_ry(l));
-        for (int l = 0; l < R; ++l) g[2 * (l + 1)] = total(a_c(R, l));
+    if (a.ansatz == QK_ANSATZ_REAL) {
+        // d alpha / d theta_l = -1, / d pb_l = 1, / d pw_l = x for every layer l
+        const float s1 = (a.gtheta || a.gpb) ? total(0) : 0.f;
+        const float s2 = a.gpw ? total(1) : 0.f;
+        for (int l = 0; l < R; ++l) {
+            if (a.gtheta) a.gtheta[e * R + l] = -s1;
+            if (a.gpb) a.gpb[e * R + l] = ptr ? s1 : 0.f;
+            if (a.gpw) a.gpw[e * R + l] = ptr ? s2 : 0.f;
+        }
+    } else if (a.ansatz == QK_ANSATZ_RPZ) {
+        if (a.gtheta) {
+            float* g = a.gtheta + e * (R + 1);
+            for (int l = 0; l < R; ++l) g[l] = total(a_ry(l));
+            g[R] = total(a_ry(RK));
+        }
+        if (a.gpb)
+            for (int l = 0; l < R; ++l) a.gpb[e * R + l] = total(a_c(RK, l));
+        if (a.gpw)
+            for (int l = 0; l < R; ++l) a.gpw[e * R + l] = total(a_pwx(RK, l));
+    } else {
+        if (a.gtheta) {
+            float* g = a.gtheta + e * (R + 1) * 2;
+            g[0] = total(a_t00(RK));
+            for (int l = 0; l < R; ++l) g[2 * l + 1] = total(a_ry(l));
+            g[2 * R + 1] = total(a_ry(RK));
+            for (int l = 0; l < R; ++l) g[2 * (l + 1)] = total(a_c(RK, l));
+        }
+        if (a.gpb)
+            for (int l = 0; l < R; ++l) a.gpb[e * R + l] = ptr ? total(a_c(RK, l)) : 0.f;
+        if (a.gpw)
+            for (int l = 0; l < R; ++l) a.gpw[e * R + l] = ptr ? total(a_pwx(RK, l)) : 0.f;
     }
-    if (a.gpb)
-        for (int l = 0; l < R; ++l) a.gpb[e * R + l] = ptr ? total(a_c(R, l)) : 0.f;
-    if (a.gpw)
-        for (int l = 0; l < R; ++l) a.gpw[e * R + l] = ptr ? total(a_pwx(R, l)) : 0.f;
     if (a.gpostw || a.gpostb || a.gbasew) {
         float cs = 0.f;
         if (use_pb && a.colsum)
@@ -129,13 +179,13 @@ __global__ void finish_grads_kernel(FinishArgs a) {
         float m = a.mask ? ld_param(a.mask, a.param_dtype, e) : 1.f;
         if (a.gpostw) {
             float pbv = use_pb ? ld_param(a.postb, a.param_dtype, e) : 0.f;
-            a.gpostw[e] = m * fmaf(pbv, cs, total(a_w(R)));
+            a.gpostw[e] = m * fmaf(pbv, cs, total(a_w(RK)));
         }
         if (a.gpostb) {
             float w = a.postw ? ld_param(a.postw, a.param_dtype, e) * m : 1.f;
             a.gpostb[e] = use_pb ? w * cs : 0.f;
         }
-        if (a.gbasew) a.gbasew[e] = a.has_base ? m * total(a_bw(R)) : 0.f;
+        if (a.gbasew) a.gbasew[e] = a.has_base ? m * total(a_bw(RK)) : 0.f;
     }
 }
 

@@ -50,10 +50,23 @@ def _f32c(t: torch.Tensor) -> torch.Tensor:
     return t.detach().to(torch.float32).contiguous()
 
 
-def _flags(preact_trainable: bool, fast_measure: bool, use_postact_bias: bool) -> int:
+def _flags(preact_trainable: bool, fast_measure: bool, use_postact_bias: bool, precise: bool = False) -> int:
     return ((_abi.QK_PREACT_TRAINABLE if preact_trainable else 0)
             | (_abi.QK_FAST_MEASURE if fast_measure else 0)
-            | (_abi.QK_USE_POSTACT_BIAS if use_postact_bias else 0))
+            | (_abi.QK_USE_POSTACT_BIAS if use_postact_bias else 0)
+            | (_abi.QK_PRECISE_MATH if precise else 0))
+
+
+# Layers up to this many edge evaluations per call default to the full-precision math path when
+# `precise="auto"`: they cost microseconds either way, and small fits are where LBFGS needs smooth gradients.
+AUTO_PRECISE_MAX_EDGES = 1 << 22
+
+
+def resolve_precise(precise, x: torch.Tensor, out_dim: int) -> bool:
+    """Turn True / False / "auto" into the flag: auto = float32 activations and a small layer."""
+    if precise == "auto" or precise is None:
+        return x.dtype == torch.float32 and x.shape[0] * x.shape[1] * out_dim <= AUTO_PRECISE_MAX_EDGES
+    return bool(precise)
 
 
 def _oi_params(postw, postb, basew, mask):
@@ -64,25 +77,38 @@ def _oi_params(postw, postb, basew, mask):
     return conv(postw), conv(postb), conv(basew), conv(mask), (_abi.QK_BF16 if dt == torch.bfloat16 else _abi.QK_F32)
 
 
-def _make_desc(x, theta, flags, param_dtype) -> _abi.QkDesc:
+def _ansatz_code(ansatz) -> int:
+    try:
+        return _abi.ANSATZ_CODES[ansatz]
+    except (KeyError, TypeError):
+        raise NotImplementedError(
+            f"ansatz {ansatz!r}: the B200 kernels implement pz_encoding, rpz_encoding and real") from None
+
+
+def _make_desc(x, theta, flags, param_dtype, ansatz="pz_encoding") -> _abi.QkDesc:
+    """Descriptor from the tensor shapes; theta is (O,I,R+1,2) pz, (O,I,R+1,1) rpz, (O,I,R,1) real."""
+    code = _ansatz_code(ansatz)
     B, I = x.shape
-    O, I2, R1, two = theta.shape
-    if I2 != I or two != 2:
-        raise ValueError(f"theta {tuple(theta.shape)} does not match x {tuple(x.shape)} "
-                         "(expected (out_dim, in_dim, reps+1, 2))")
-    return _abi.QkDesc(B, I, O, R1 - 1, _io_dtype(x), param_dtype, flags, 0)
+    if theta.dim() != 4:
+        raise ValueError(f"theta must have 4 dimensions, got {tuple(theta.shape)}")
+    O, I2, layers, width = theta.shape
+    if I2 != I or width != (2 if code == _abi.QK_ANSATZ_PZ else 1):
+        raise ValueError(f"theta {tuple(theta.shape)} does not match x {tuple(x.shape)} for ansatz {ansatz!r}")
+    reps = layers if code == _abi.QK_ANSATZ_REAL else layers - 1
+    return _abi.QkDesc(B, I, O, reps, _io_dtype(x), param_dtype, flags, code)
 
 
 def layer_forward(x, theta, pw, pb, postw, postb=None, basew=None, mask=None, *,
                   preact_trainable: bool, fast_measure: bool = True,
-                  use_postact_bias: bool = False) -> torch.Tensor:
+                  use_postact_bias: bool = False, ansatz: str = "pz_encoding",
+                  precise: bool = False) -> torch.Tensor:
     """``y (B,O)`` of the fused layer; no autograd (see ``qkan_layer``)."""
     lib = _abi.load()
     _require_cuda(x, "x")
     x = x.detach().contiguous()
     theta, pw, pb = _f32c(theta), _f32c(pw), _f32c(pb)
     postw, postb, basew, mask, pdt = _oi_params(postw, postb if use_postact_bias else None, basew, mask)
-    desc = _make_desc(x, theta, _flags(preact_trainable, fast_measure, use_postact_bias and postb is not None), pdt)
+    desc = _make_desc(x, theta, _flags(preact_trainable, fast_measure, use_postact_bias and postb is not None, precise), pdt, ansatz)
     y = torch.empty((x.shape[0], theta.shape[0]), dtype=x.dtype, device=x.device)
     with torch.cuda.device(x.device):
         nbytes = lib.qk_forward_workspace_bytes(_abi.desc_pointer(desc))
@@ -97,7 +123,8 @@ def layer_forward(x, theta, pw, pb, postw, postb=None, basew=None, mask=None, *,
 def layer_backward(x, theta, pw, pb, postw, postb, basew, mask, gy, *, preact_trainable: bool,
                    fast_measure: bool = True, use_postact_bias: bool = False,
                    want=("x", "theta", "preacts_weight", "preacts_bias", "postact_weights",
-                         "postact_bias", "base_weight"), out: Optional[dict] = None) -> dict:
+                         "postact_bias", "base_weight"), out: Optional[dict] = None,
+                   ansatz: str = "pz_encoding", precise: bool = False) -> dict:
     """Gradients of ``sum(y * gy)`` named as the reference's parameters; float32 except ``x``.
 
     ``out`` may hold preallocated contiguous destination tensors by name (for example the views
@@ -109,11 +136,11 @@ def layer_backward(x, theta, pw, pb, postw, postb, basew, mask, gy, *, preact_tr
     gy = gy.detach().to(x.dtype).contiguous()
     theta, pw, pb = _f32c(theta), _f32c(pw), _f32c(pb)
     postw, postb, basew, mask, pdt = _oi_params(postw, postb if use_postact_bias else None, basew, mask)
-    desc = _make_desc(x, theta, _flags(preact_trainable, fast_measure, use_postact_bias and postb is not None), pdt)
-    O, I, R1, _ = theta.shape
+    desc = _make_desc(x, theta, _flags(preact_trainable, fast_measure, use_postact_bias and postb is not None, precise), pdt, ansatz)
+    O, I = theta.shape[:2]
     dev = x.device
-    shapes = {"x": tuple(x.shape), "theta": (O, I, R1, 2), "preacts_weight": (O, I, R1 - 1),
-              "preacts_bias": (O, I, R1 - 1), "postact_weights": (O, I), "postact_bias": (O, I),
+    shapes = {"x": tuple(x.shape), "theta": tuple(theta.shape), "preacts_weight": (O, I, desc.reps),
+              "preacts_bias": (O, I, desc.reps), "postact_weights": (O, I), "postact_bias": (O, I),
               "base_weight": (O, I)}
     given = out or {}
     out = {}
@@ -140,13 +167,14 @@ def layer_backward(x, theta, pw, pb, postw, postb, basew, mask, gy, *, preact_tr
     return out
 
 
-def postacts_forward(x, theta, pw, pb, *, preact_trainable: bool, fast_measure: bool = True) -> torch.Tensor:
+def postacts_forward(x, theta, pw, pb, *, preact_trainable: bool, fast_measure: bool = True,
+                     ansatz: str = "pz_encoding", precise: bool = False) -> torch.Tensor:
     """Per-edge activations ``(B,O,I)`` (solver contract); no autograd."""
     lib = _abi.load()
     _require_cuda(x, "x")
     x = x.detach().contiguous()
     theta, pw, pb = _f32c(theta), _f32c(pw), _f32c(pb)
-    desc = _make_desc(x, theta, _flags(preact_trainable, fast_measure, False), _abi.QK_F32)
+    desc = _make_desc(x, theta, _flags(preact_trainable, fast_measure, False, precise), _abi.QK_F32, ansatz)
     out = torch.empty((x.shape[0], theta.shape[0], x.shape[1]), dtype=x.dtype, device=x.device)
     with torch.cuda.device(x.device):
         nbytes = lib.qk_forward_workspace_bytes(_abi.desc_pointer(desc))
@@ -160,24 +188,25 @@ def postacts_forward(x, theta, pw, pb, *, preact_trainable: bool, fast_measure: 
 
 def postacts_backward(x, theta, pw, pb, gpostacts, *, preact_trainable: bool,
                       fast_measure: bool = True,
-                      want=("x", "theta", "preacts_weight", "preacts_bias")) -> dict:
+                      want=("x", "theta", "preacts_weight", "preacts_bias"),
+                      ansatz: str = "pz_encoding", precise: bool = False) -> dict:
     lib = _abi.load()
     _require_cuda(x, "x")
     x = x.detach().contiguous()
     gpostacts = gpostacts.detach().to(x.dtype).contiguous()
     theta, pw, pb = _f32c(theta), _f32c(pw), _f32c(pb)
-    desc = _make_desc(x, theta, _flags(preact_trainable, fast_measure, False), _abi.QK_F32)
-    O, I, R1, _ = theta.shape
+    desc = _make_desc(x, theta, _flags(preact_trainable, fast_measure, False, precise), _abi.QK_F32, ansatz)
+    O, I = theta.shape[:2]
     f32 = dict(dtype=torch.float32, device=x.device)
     out = {}
     if "x" in want:
         out["x"] = torch.empty_like(x)
     if "theta" in want:
-        out["theta"] = torch.empty((O, I, R1, 2), **f32)
+        out["theta"] = torch.empty(tuple(theta.shape), **f32)
     if "preacts_weight" in want:
-        out["preacts_weight"] = torch.empty((O, I, R1 - 1), **f32)
+        out["preacts_weight"] = torch.empty((O, I, desc.reps), **f32)
     if "preacts_bias" in want:
-        out["preacts_bias"] = torch.empty((O, I, R1 - 1), **f32)
+        out["preacts_bias"] = torch.empty((O, I, desc.reps), **f32)
     with torch.cuda.device(x.device):
         nbytes = lib.qk_backward_workspace_bytes(_abi.desc_pointer(desc))
         ws = _workspace(x.device, nbytes)
@@ -190,25 +219,30 @@ def postacts_backward(x, theta, pw, pb, gpostacts, *, preact_trainable: bool,
     return out
 
 
+def _uses_preacts(preact_trainable: bool, ansatz: str) -> bool:
+    """rpz always encodes pw*x + pb, so its preact gradients exist whatever the flag says."""
+    return preact_trainable or _ansatz_code(ansatz) == _abi.QK_ANSATZ_RPZ
+
+
 class _LayerFunction(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, theta, pw, pb, postw, postb, basew, mask, preact_trainable, fast_measure,
-                use_postact_bias):
+                use_postact_bias, ansatz, precise):
         ctx.save_for_backward(x, theta, pw, pb, postw, postb, basew, mask)
-        ctx.cfg = (preact_trainable, fast_measure, use_postact_bias)
+        ctx.cfg = (preact_trainable, fast_measure, use_postact_bias, ansatz, precise)
         return layer_forward(x, theta, pw, pb, postw, postb, basew, mask,
                              preact_trainable=preact_trainable, fast_measure=fast_measure,
-                             use_postact_bias=use_postact_bias)
+                             use_postact_bias=use_postact_bias, ansatz=ansatz, precise=precise)
 
     @staticmethod
     def backward(ctx, gy):
         x, theta, pw, pb, postw, postb, basew, mask = ctx.saved_tensors
-        preact_trainable, fast_measure, use_postact_bias = ctx.cfg
+        preact_trainable, fast_measure, use_postact_bias, ansatz, precise = ctx.cfg
         names = ("x", "theta", "preacts_weight", "preacts_bias", "postact_weights", "postact_bias",
                  "base_weight")
         need = ctx.needs_input_grad
         want = tuple(n for k, n in enumerate(names) if need[k])
-        if not preact_trainable:
+        if not _uses_preacts(preact_trainable, ansatz):
             want = tuple(n for n in want if n not in ("preacts_weight", "preacts_bias"))
         if postb is None or not use_postact_bias:
             want = tuple(n for n in want if n != "postact_bias")
@@ -216,7 +250,7 @@ class _LayerFunction(torch.autograd.Function):
             want = tuple(n for n in want if n != "base_weight")
         g = layer_backward(x, theta, pw, pb, postw, postb, basew, mask, gy,
                            preact_trainable=preact_trainable, fast_measure=fast_measure,
-                           use_postact_bias=use_postact_bias, want=want)
+                           use_postact_bias=use_postact_bias, want=want, ansatz=ansatz, precise=precise)
         srcs = (x, theta, pw, pb, postw, postb, basew)
         outs = []
         for k, n in enumerate(names):
@@ -224,37 +258,41 @@ class _LayerFunction(torch.autograd.Function):
             if t is not None and srcs[k] is not None:
                 t = t.to(srcs[k].dtype).reshape(srcs[k].shape)
             outs.append(t)
-        return (*outs, None, None, None, None)
+        return (*outs, None, None, None, None, None, None)
 
 
 def qkan_layer(x, theta, preacts_weight, preacts_bias, postact_weights, postact_bias=None,
                base_weight=None, mask=None, *, preact_trainable: bool, fast_measure: bool = True,
-               use_postact_bias: bool = False) -> torch.Tensor:
-    """Differentiable fused QKAN layer ``(B,I) -> (B,O)`` on the CUDA kernels."""
+               use_postact_bias: bool = False, ansatz: str = "pz_encoding", precise="auto") -> torch.Tensor:
+    """Differentiable fused QKAN layer ``(B,I) -> (B,O)`` on the CUDA kernels.
+
+    ``precise``: True / False / "auto" (see ``resolve_precise``) selects full-precision sin/cos/sqrt
+    instead of the special-function unit.
+    """
     return _LayerFunction.apply(x, theta, preacts_weight, preacts_bias, postact_weights,
                                 postact_bias, base_weight, mask, preact_trainable, fast_measure,
-                                use_postact_bias)
+                                use_postact_bias, ansatz, resolve_precise(precise, x, theta.shape[0]))
 
 
 class _PostactsFunction(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, theta, pw, pb, preact_trainable, fast_measure):
+    def forward(ctx, x, theta, pw, pb, preact_trainable, fast_measure, ansatz, precise):
         ctx.save_for_backward(x, theta, pw, pb)
-        ctx.cfg = (preact_trainable, fast_measure)
+        ctx.cfg = (preact_trainable, fast_measure, ansatz, precise)
         return postacts_forward(x, theta, pw, pb, preact_trainable=preact_trainable,
-                                fast_measure=fast_measure)
+                                fast_measure=fast_measure, ansatz=ansatz, precise=precise)
 
     @staticmethod
     def backward(ctx, gpa):
         x, theta, pw, pb = ctx.saved_tensors
-        preact_trainable, fast_measure = ctx.cfg
+        preact_trainable, fast_measure, ansatz, precise = ctx.cfg
         names = ("x", "theta", "preacts_weight", "preacts_bias")
         need = ctx.needs_input_grad
         want = tuple(n for k, n in enumerate(names) if need[k])
-        if not preact_trainable:
+        if not _uses_preacts(preact_trainable, ansatz):
             want = tuple(n for n in want if n not in ("preacts_weight", "preacts_bias"))
         g = postacts_backward(x, theta, pw, pb, gpa, preact_trainable=preact_trainable,
-                              fast_measure=fast_measure, want=want)
+                              fast_measure=fast_measure, want=want, ansatz=ansatz, precise=precise)
         srcs = (x, theta, pw, pb)
         outs = []
         for k, n in enumerate(names):
@@ -262,11 +300,11 @@ class _PostactsFunction(torch.autograd.Function):
             if t is not None:
                 t = t.to(srcs[k].dtype).reshape(srcs[k].shape)
             outs.append(t)
-        return (*outs, None, None)
+        return (*outs, None, None, None, None)
 
 
 def qkan_postacts(x, theta, preacts_weight, preacts_bias, *, preact_trainable: bool,
-                  fast_measure: bool = True) -> torch.Tensor:
+                  fast_measure: bool = True, ansatz: str = "pz_encoding", precise="auto") -> torch.Tensor:
     """Differentiable per-edge activations ``(B,O,I)`` — the reference solver contract."""
     return _PostactsFunction.apply(x, theta, preacts_weight, preacts_bias, preact_trainable,
-                                   fast_measure)
+                                   fast_measure, ansatz, resolve_precise(precise, x, theta.shape[0]))

@@ -24,6 +24,8 @@ from . import functional as qf
 
 SOLVER_NAME = "b200"
 _PZ = ("pz_encoding", "pz")
+_RPZ = ("rpz_encoding", "rpz")
+_SUPPORTED_ANSATZ = _PZ + _RPZ + ("real",)
 _ACTIVATIONS = {
     "silu": nn.SiLU, "swish": nn.SiLU,
     "gelu": lambda: nn.GELU(approximate="none"), "gelu_exact": lambda: nn.GELU(approximate="none"),
@@ -66,9 +68,9 @@ class QKANLayer(nn.Module):
         super().__init__()
         if p_dim not in (2, 4):
             raise ValueError(f"p_dim must be 2 or 4, got {p_dim}")
-        if callable(ansatz) or ansatz not in _PZ:
+        if callable(ansatz) or ansatz not in _SUPPORTED_ANSATZ:
             raise NotImplementedError(
-                f"ansatz {ansatz!r}: the B200 kernels implement 'pz_encoding' only")
+                f"ansatz {ansatz!r}: the B200 kernels implement pz_encoding, rpz_encoding and real")
         self.p_dim = p_dim
         self.solver_kwargs = solver_kwargs or {}
         self.checkpoint_reps = checkpoint_reps  # accepted for compatibility; nothing is checkpointed here
@@ -105,18 +107,27 @@ class QKANLayer(nn.Module):
         _seed_everything(self.seed)
         group, reps, dev, dt = self.group, self.reps, self.device, self.p_dtype
         self.group_count = int(np.prod(group))
-        self._theta_natural_shape = (*group, reps + 1, 2)
+        # theta layers x gates per layer, as in the reference (src/qkan/qkan.py:265-274)
+        if self.ansatz in _PZ:
+            self._theta_natural_shape = (*group, reps + 1, 2)
+        elif self.ansatz in _RPZ:
+            self._theta_natural_shape = (*group, reps + 1, 1)
+        else:  # "real": no final layer; the reference also pins its compute dtype to bfloat16 here
+            self._theta_natural_shape = (*group, reps, 1)
+            self.c_dtype = torch.bfloat16
         self._preacts_natural_shape = (*group, reps)
         flat = self.p_dim == 2
-        theta_shape = (self.group_count, (reps + 1) * 2) if flat else self._theta_natural_shape
+        theta_shape = ((self.group_count, self._theta_natural_shape[-2] * self._theta_natural_shape[-1])
+                       if flat else self._theta_natural_shape)
         pre_shape = (self.group_count, reps) if flat else self._preacts_natural_shape
         oi_shape = (self.out_dim * self.in_dim,) if flat else (self.out_dim, self.in_dim)
 
         self.theta = nn.Parameter(torch.empty(*theta_shape, device=dev, dtype=dt))
         self.preacts_weight = nn.Parameter(torch.ones(*pre_shape, device=dev, dtype=dt),
                                            requires_grad=self.preact_trainable)
+        # rpz always trains its encoding bias (src/qkan/qkan.py:292-295)
         self.preacts_bias = nn.Parameter(torch.zeros(*pre_shape, device=dev, dtype=dt),
-                                         requires_grad=self.preact_trainable)
+                                         requires_grad=self.preact_trainable or self.ansatz in _RPZ)
         if self.ba_trainable:
             self.base_weight = nn.Parameter(0.5 * torch.ones(*oi_shape, device=dev, dtype=dt))
         else:
@@ -262,7 +273,7 @@ class QKANLayer(nn.Module):
             self._as_oi(self.postact_bias) if use_pb else None,
             base_w if (has_base and silu_base) else None, mask,
             preact_trainable=self.preact_trainable, fast_measure=self.fast_measure,
-            use_postact_bias=use_pb)
+            use_postact_bias=use_pb, ansatz=self.ansatz, precise=self.solver_kwargs.get("precise", "auto"))
         if has_base and not silu_base:
             # other base activations stay a plain library GEMM beside the kernel (qkan.py:755, 784)
             w = base_w if mask is None else base_w * mask
@@ -276,7 +287,9 @@ class QKANLayer(nn.Module):
         self._check_solver()
         theta, pw, pb = self._expanded()
         postacts = qf.postacts_forward(x, theta, pw, pb, preact_trainable=self.preact_trainable,
-                                       fast_measure=self.fast_measure).to(self.p_dtype)
+                                       fast_measure=self.fast_measure, ansatz=self.ansatz,
+                                       precise=qf.resolve_precise(self.solver_kwargs.get("precise", "auto"), x,
+                                                                  self.out_dim)).to(self.p_dtype)
         base = torch.einsum("oi,bi->boi", self._as_oi(self.base_weight), self.base_activation(x))
         return ((postacts + self._as_oi(self.postact_bias)) * self._as_oi(self.postact_weights)[None]
                 + base) * self._as_oi(self.mask)[None]

@@ -13,18 +13,19 @@ import torch
 
 from . import functional as qf
 
-_PZ = ("pz_encoding", "pz")
+_SUPPORTED = ("pz_encoding", "pz", "rpz_encoding", "rpz", "real")
 
 
 class B200Solver:
-    """``solver="b200"``: per-edge activations of the pz ansatz on the sm_100a kernels."""
+    """``solver="b200"``: per-edge activations (pz, rpz and real ansaetze) on the sm_100a kernels."""
 
     name = "b200"
 
     def __call__(self, x, theta, preacts_weight, preacts_bias, reps, **kwargs) -> torch.Tensor:
         ansatz = kwargs.get("ansatz", "pz_encoding")
-        if callable(ansatz) or ansatz not in _PZ:
-            raise NotImplementedError(f"the b200 solver implements 'pz_encoding' only, got {ansatz!r}")
+        if callable(ansatz) or ansatz not in _SUPPORTED:
+            raise NotImplementedError(
+                f"the b200 solver implements pz_encoding, rpz_encoding and real, got {ansatz!r}")
         trainable = kwargs.get("preacts_trainable", False)
         fast = kwargs.get("fast_measure", True)
         batch, in_dim = x.shape
@@ -43,10 +44,11 @@ class B200Solver:
             rep_out = out_dim if preacts_weight.shape[0] == 1 else 1
             preacts_weight = preacts_weight.repeat(rep_out, rep_in, 1)[:, :in_dim]
             preacts_bias = preacts_bias.repeat(rep_out, rep_in, 1)[:, :in_dim]
-        if theta.shape[2] != reps + 1:
-            raise ValueError(f"theta holds {theta.shape[2] - 1} repetitions, reps={reps}")
+        layers = reps if ansatz == "real" else reps + 1
+        if theta.shape[2] != layers:
+            raise ValueError(f"theta holds {theta.shape[2]} layers, reps={reps} needs {layers}")
         return qf.qkan_postacts(x, theta, preacts_weight, preacts_bias, preact_trainable=trainable,
-                                fast_measure=fast)
+                                fast_measure=fast, ansatz=ansatz, precise=kwargs.get("precise", "auto"))
 
 
 _REGISTRY: dict = {}

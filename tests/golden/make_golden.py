@@ -3,7 +3,7 @@
 Usage (only where the reference checkout is mounted; the fixtures are committed so
 nothing at test time needs it):
 
-    python tests/golden/make_golden.py /path/to/reference
+    python tests/golden/make_golden.py /path/to/reference [layer|ansatz|init|fit]
 
 The reference package imports ``matplotlib`` unconditionally (``src/qkan/qkan.py:33``)
 for its plotting helpers; an empty stand-in module is registered before the import,
@@ -15,6 +15,9 @@ What is written:
   reference ``exact`` solver in complex128/float64: the inputs, ``y``, the per-edge
   ``postacts`` and every gradient of ``sum(y * gy)`` from torch autograd; plus ``y`` from
   the reference's default complex64/float32 arithmetic.
+* ``ansatz_cases.npz`` — the same for the ``rpz_encoding`` and ``real`` ansaetze, with the solver called
+  directly in float64 (the reference layer forces bfloat16 arithmetic for ``real``, ``qkan.py:272-274``)
+  and the epilogue of ``qkan.py:776-785`` applied on top.
 * ``init_cases.npz`` — seeded parameter initialisations (``state_dict`` tensors).
 * ``fit_case.npz`` — the 1-D function-fit configuration: dataset, seeded initial
   prediction / loss / gradients, and the LBFGS loss trajectory of the reference.
@@ -112,6 +115,55 @@ def layer_cases(qkan, torch):
     np.savez_compressed(os.path.join(HERE, "layer_cases.npz"), **out)
 
 
+# name, ansatz, B, I, O, R, preact_trainable, fast_measure
+ANSATZ_CASES = [
+    ("rpz_r1_fast", "rpz_encoding", 6, 3, 4, 1, True, True),
+    ("rpz_r3_fixed", "rpz_encoding", 5, 4, 3, 3, False, True),
+    ("rpz_r2_born", "rpz_encoding", 7, 2, 5, 2, True, False),
+    ("rpz_r5_wide", "rpz_encoding", 4, 35, 3, 5, True, True),
+    ("real_r1_fast", "real", 6, 3, 4, 1, True, True),
+    ("real_r2_fixed", "real", 5, 4, 3, 2, False, True),
+    ("real_r4_born", "real", 7, 2, 5, 4, True, False),
+    ("real_r3_wide", "real", 4, 35, 3, 3, False, False),
+]
+
+
+def ansatz_cases(qkan, torch):
+    out = {}
+    solver = qkan.solver.get_solver("exact")
+    for idx, (name, ansatz, B, I, O, R, ptr, fast) in enumerate(ANSATZ_CASES):
+        g = torch.Generator().manual_seed(2000 + idx)
+        rnd = lambda *s: torch.rand(*s, generator=g, dtype=torch.float64)  # noqa: E731
+        nrm = lambda *s: torch.randn(*s, generator=g, dtype=torch.float64)  # noqa: E731
+        is_real = ansatz == "real"
+        th_shape = (O, I, R, 1) if is_real else (O, I, R + 1, 1)
+        leaf = lambda t: t.clone().requires_grad_(True)  # noqa: E731
+        x = leaf(rnd(B, I) * 4 - 2)
+        theta = leaf((rnd(*th_shape) * 2 - 1) * np.pi)
+        pw = leaf(1 + 0.3 * nrm(O, I, R))
+        pb = leaf(0.3 * nrm(O, I, R))
+        postw = leaf(nrm(O, I) / np.sqrt(I))
+        postb = leaf(0.5 * nrm(O, I))
+        basew = leaf(0.5 * nrm(O, I))
+        mask = (rnd(O, I) > 0.3).double()
+        gy = nrm(B, O)
+        pa = solver(x, theta, pw, pb, R, ansatz=ansatz, preacts_trainable=ptr, fast_measure=fast,
+                    out_dim=O, dtype=torch.float64 if is_real else torch.complex128)
+        y = ((pa + postb) * (postw * mask)).sum(dim=2) + torch.nn.functional.silu(x) @ (basew * mask).T
+        (y * gy).sum().backward()
+        zero = lambda t: t.grad if t.grad is not None else torch.zeros_like(t)  # noqa: E731
+        for k, v in dict(in_x=x, in_theta=theta, in_preacts_weight=pw, in_preacts_bias=pb,
+                         in_postact_weights=postw, in_postact_bias=postb, in_base_weight=basew,
+                         in_mask=mask, in_gy=gy, y=y, postacts=pa, g_x=zero(x), g_theta=zero(theta),
+                         g_preacts_weight=zero(pw), g_preacts_bias=zero(pb), g_postact_weights=zero(postw),
+                         g_postact_bias=zero(postb), g_base_weight=zero(basew)).items():
+            out[f"{name}/{k}"] = v.detach().numpy()
+        out[f"{name}/flags"] = np.array([int(ptr), int(fast)], dtype=np.int64)
+        out[f"{name}/ansatz"] = np.array(ansatz)
+    out["names"] = np.array([c[0] for c in ANSATZ_CASES])
+    np.savez_compressed(os.path.join(HERE, "ansatz_cases.npz"), **out)
+
+
 def init_cases(qkan, torch):
     out = {}
     specs = {
@@ -163,9 +215,15 @@ def main():
 
     torch.set_num_threads(max(1, os.cpu_count() or 1))
     qkan = _import_reference(ref_root)
-    layer_cases(qkan, torch)
-    init_cases(qkan, torch)
-    fit_case(qkan, torch)
+    only = sys.argv[2] if len(sys.argv) > 2 else "all"
+    if only in ("all", "layer"):
+        layer_cases(qkan, torch)
+    if only in ("all", "ansatz"):
+        ansatz_cases(qkan, torch)
+    if only in ("all", "init"):
+        init_cases(qkan, torch)
+    if only in ("all", "fit"):
+        fit_case(qkan, torch)
     print("wrote", sorted(p for p in os.listdir(HERE) if p.endswith(".npz")))
 
 

@@ -10,12 +10,13 @@ from tests.util import GOLDEN, GRAD_NAMES, TOL_BF16, TOL_F32, case_inputs, golde
 pytestmark = pytest.mark.gpu
 
 
-def _layer_from_case(case, p_dim=4):
+def _layer_from_case(case, p_dim=4, precise="auto"):
     B, I, O, R = (int(v) for v in case["dims"])
     cfg = case["cfg"]
     layer = QKANLayer(I, O, reps=R, device="cuda", preact_trainable=cfg["preact_trainable"],
                       postact_weight_trainable=True, postact_bias_trainable=cfg["use_postact_bias"],
-                      ba_trainable=case["base"], fast_measure=cfg["fast_measure"], p_dim=p_dim)
+                      ba_trainable=case["base"], fast_measure=cfg["fast_measure"], p_dim=p_dim,
+                      solver_kwargs={"precise": precise})
     with torch.no_grad():
         for name in ("theta", "preacts_weight", "preacts_bias", "postact_weights", "postact_bias",
                      "base_weight", "mask"):
@@ -25,10 +26,10 @@ def _layer_from_case(case, p_dim=4):
     return layer
 
 
-@pytest.mark.parametrize("p_dim", [4, 2])
+@pytest.mark.parametrize("p_dim,precise", [(4, False), (2, "auto")])
 @pytest.mark.parametrize("case", golden_layer_cases(), ids=lambda c: c["name"])
-def test_layer_autograd_matches_reference(case, p_dim):
-    layer = _layer_from_case(case, p_dim).train()
+def test_layer_autograd_matches_reference(case, p_dim, precise):
+    layer = _layer_from_case(case, p_dim, precise).train()
     x = torch.as_tensor(case["in_x"], dtype=torch.float32, device="cuda").requires_grad_(True)
     gy = torch.as_tensor(case["in_gy"], dtype=torch.float32, device="cuda")
     y = layer(x)
@@ -125,7 +126,7 @@ def test_mlp_with_bf16_activations_and_sequence_axis():
     twin = QKAN([16, 24, 8], reps=2, seed=4, device="cuda")
     twin.load_state_dict({k: v.float() for k, v in model.state_dict().items()})
     y32 = twin(x.float())
-    assert nerr(y.float().cpu().numpy(), y32.detach().cpu().numpy()) <= 2 * TOL_BF16
+    assert nerr(y.detach().float().cpu().numpy(), y32.detach().cpu().numpy()) <= 2 * TOL_BF16
     y.float().sum().backward()
     assert all(p.grad is not None and p.grad.dtype == torch.bfloat16
                for p in model.parameters() if p.requires_grad)

@@ -4,8 +4,8 @@ import pytest
 import torch
 
 from oracle import oracle
-from tests.util import (GRAD_NAMES, TOL_BF16, TOL_F32, case_inputs, golden_layer_cases, nerr,
-                        random_problem)
+from tests.util import (GRAD_NAMES, TOL_BF16, TOL_F32, ansatz_case_inputs, case_inputs,
+                        golden_ansatz_cases, golden_layer_cases, nerr, random_problem)
 
 pytestmark = pytest.mark.gpu
 
@@ -14,17 +14,41 @@ def _dev(a, dtype=torch.float32):
     return None if a is None else torch.as_tensor(np.asarray(a), dtype=dtype, device="cuda")
 
 
-def _run_cuda(p, cfg, io_dtype=torch.float32, param_dtype=torch.float32):
+def _run_cuda(p, cfg, io_dtype=torch.float32, param_dtype=torch.float32, precise=False):
     from qkan_b200 import functional as F
 
     x = _dev(p["x"], io_dtype)
     gy = _dev(p["gy"], io_dtype)
     th, pw, pb = _dev(p["theta"]), _dev(p["pw"]), _dev(p["pb"])
     postw, postb, basew, mask = (_dev(p[k], param_dtype) for k in ("postw", "postb", "basew", "mask"))
-    y = F.layer_forward(x, th, pw, pb, postw, postb, basew, mask, **cfg)
-    g = F.layer_backward(x, th, pw, pb, postw, postb, basew, mask, gy, **cfg)
+    y = F.layer_forward(x, th, pw, pb, postw, postb, basew, mask, precise=precise, **cfg)
+    g = F.layer_backward(x, th, pw, pb, postw, postb, basew, mask, gy, precise=precise, **cfg)
     torch.cuda.synchronize()
     return y.float().cpu().numpy(), {k: v.float().cpu().numpy() for k, v in g.items()}
+
+
+@pytest.mark.parametrize("case", golden_ansatz_cases(), ids=lambda c: c["name"])
+def test_golden_rpz_and_real_cases_fp32(case):
+    """rpz_encoding and real ansaetze: CUDA fp32 vs the reference's float64 outputs."""
+    p = ansatz_case_inputs(case)
+    for precise in (False, True):
+        y, g = _run_cuda(p, case["cfg"], precise=precise)
+        _check(y, g, case["y"], {k: case["g_" + k] for k in GRAD_NAMES}, TOL_F32, case["name"])
+
+
+@pytest.mark.parametrize("ansatz,B,I,O,R", [("pz", 70, 33, 20, 9), ("pz", 40, 64, 12, 12), ("pz", 33, 20, 9, 16),
+                                             ("rpz", 50, 40, 17, 11), ("rpz", 300, 70, 33, 3), ("real", 300, 70, 33, 5),
+                                             ("real", 64, 5, 3, 16)])
+def test_long_circuits_and_other_ansaetze_vs_oracle(ansatz, B, I, O, R):
+    """Repetition counts above 8 run in the padded 12 / 16 instantiations; rpz and real at larger sizes."""
+    p = random_problem(B + R, B, I, O, R, use_pb=True, base=True, masked=True)
+    layers, width = {"pz": (R + 1, 2), "rpz": (R + 1, 1), "real": (R, 1)}[ansatz]
+    rng = np.random.default_rng(R)
+    p["theta"] = rng.uniform(-np.pi, np.pi, (O, I, layers, width)).astype(np.float32)
+    cfg = dict(preact_trainable=(R % 2 == 1), fast_measure=(R % 3 != 0), use_postact_bias=True, ansatz=ansatz)
+    y, g = _run_cuda(p, cfg)
+    y_ref, g_ref = _run_oracle(p, cfg)
+    _check(y, g, y_ref, g_ref, TOL_F32, f"{ansatz} B{B} I{I} O{O} R{R}")
 
 
 def _run_oracle(p, cfg):
@@ -40,13 +64,14 @@ def _check(y, g, y_ref, g_ref, tol, label):
         assert nerr(g[k], g_ref[k]) <= tol, f"{label}: grad {k} err {nerr(g[k], g_ref[k]):.3e}"
 
 
+@pytest.mark.parametrize("precise", [False, True], ids=["sfu", "precise"])
 @pytest.mark.parametrize("case", golden_layer_cases(), ids=lambda c: c["name"])
-def test_golden_cases_fp32(case):
-    """CUDA fp32 vs the reference's own float64 outputs stored in tests/golden."""
+def test_golden_cases_fp32(case, precise):
+    """CUDA fp32 (special-function-unit path and full-precision path) vs the reference's float64 outputs."""
     p = case_inputs(case)
-    y, g = _run_cuda(p, case["cfg"])
+    y, g = _run_cuda(p, case["cfg"], precise=precise)
     g_ref = {k: case["g_" + k] for k in GRAD_NAMES}
-    _check(y, g, case["y"], g_ref, TOL_F32, case["name"])
+    _check(y, g, case["y"], g_ref, TOL_F32 if not precise else 3e-6, case["name"])
 
 
 @pytest.mark.parametrize("B,I,O,R", [(1, 1, 1, 1), (33, 7, 5, 2), (100, 40, 33, 3), (257, 64, 64, 3),

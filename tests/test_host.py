@@ -75,7 +75,7 @@ def test_no_cpu_fallback_and_unknown_solver_or_ansatz():
     with pytest.raises(NotImplementedError):
         QKANLayer(3, 2, solver="exact")(torch.zeros(4, 3))
     with pytest.raises(NotImplementedError):
-        QKANLayer(3, 2, ansatz="rpz_encoding")
+        QKANLayer(3, 2, ansatz="px_encoding")
     with pytest.raises(ValueError):
         QKANLayer(3, 2, p_dim=3)
     assert "b200" in qkan_b200.get_registry()
@@ -108,3 +108,12 @@ def test_grad_bucket_views_alias_one_flat_buffer():
     assert float(bucket.flat.sum()) == 2.0 * 3 * 5 * 3 * 2 + 3.0 * 15
     assert all(bucket.offsets[k] % 64 == 0 for k in shapes)
     bucket.all_reduce()  # no process group: a no-op
+
+
+def test_parameter_shapes_of_the_other_ansaetze_follow_the_reference():
+    rpz = QKANLayer(4, 3, reps=2, ansatz="rpz_encoding")
+    assert rpz.theta.shape == (3, 4, 3, 1)
+    assert rpz.preacts_bias.requires_grad and not rpz.preacts_weight.requires_grad
+    real = QKANLayer(4, 3, reps=2, ansatz="real", p_dim=2)
+    assert real.theta.shape == (12, 2) and real._theta_natural().shape == (3, 4, 2, 1)
+    assert real.c_dtype == torch.bfloat16

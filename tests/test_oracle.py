@@ -3,7 +3,8 @@ import numpy as np
 import pytest
 
 from oracle import oracle
-from tests.util import GRAD_NAMES, case_inputs, golden_layer_cases, nerr
+from tests.util import (GRAD_NAMES, ansatz_case_inputs, case_inputs, golden_ansatz_cases, golden_layer_cases,
+                        nerr)
 
 
 @pytest.mark.parametrize("case", golden_layer_cases(), ids=lambda c: c["name"])
@@ -54,3 +55,17 @@ def test_oracle_rejects_too_many_reps():
     with pytest.raises(RuntimeError):
         oracle.postacts(np.zeros((1, 1)), np.zeros((1, 1, 66, 2)), np.zeros((1, 1, 65)), np.zeros((1, 1, 65)),
                         preact_trainable=True)
+
+
+@pytest.mark.parametrize("case", golden_ansatz_cases(), ids=lambda c: c["name"])
+def test_oracle_matches_reference_for_rpz_and_real(case):
+    p = ansatz_case_inputs(case)
+    args = [p[k] for k in ("x", "theta", "pw", "pb", "postw", "postb", "basew", "mask")]
+    cfg = case["cfg"]
+    assert nerr(oracle.forward(*args, **cfg), case["y"]) <= 1e-13
+    pa = oracle.postacts(*args[:4], preact_trainable=cfg["preact_trainable"], fast_measure=cfg["fast_measure"],
+                         ansatz=cfg["ansatz"])
+    assert nerr(pa, case["postacts"]) <= 1e-13
+    g = oracle.backward(*args, p["gy"], **cfg)
+    for k in GRAD_NAMES:
+        assert nerr(g[k], case["g_" + k]) <= 1e-12, k

@@ -69,3 +69,23 @@ def random_problem(seed, B, I, O, R, *, use_pb=True, base=False, masked=False, x
         gy=rng.standard_normal((B, O)),
     )
     return {k: (None if v is None else v.astype(np.float32)) for k, v in p.items()}
+
+
+def golden_ansatz_cases():
+    """rpz / real fixtures: inputs, y, postacts and all gradients from the reference (float64)."""
+    d = np.load(os.path.join(GOLDEN, "ansatz_cases.npz"))
+    cases = []
+    for name in d["names"]:
+        name = str(name)
+        g = {k.split("/", 1)[1]: d[k] for k in d.files if k.startswith(name + "/")}
+        ptr, fast = (bool(v) for v in g["flags"])
+        g["cfg"] = dict(preact_trainable=ptr, fast_measure=fast, use_postact_bias=True, ansatz=str(g["ansatz"]))
+        g["name"] = name
+        cases.append(g)
+    return cases
+
+
+def ansatz_case_inputs(g):
+    return dict(x=g["in_x"], theta=g["in_theta"], pw=g["in_preacts_weight"], pb=g["in_preacts_bias"],
+                postw=g["in_postact_weights"], postb=g["in_postact_bias"], basew=g["in_base_weight"],
+                mask=g["in_mask"], gy=g["in_gy"])
