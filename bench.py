@@ -286,17 +286,14 @@ def run_b200(args):
     hgrads = torch.empty(bucket.flat.numel(), dtype=torch.float32).pin_memory()
     e2e_steps = 0 if args.no_e2e else max(3, min(args.steps, 10))
 
+    from qkan_b200.host import HostLayerPipeline
+
+    pipe = HostLayerPipeline(rows, IN_DIM, OUT_DIM, REPS, dev, n_chunks=args.e2e_chunks) if e2e_steps else None
+    dev_params = {k: t[k] for k in ("theta", "pw", "pb", "postw", "postb")}
+
     def e2e_step():
-        dx = hx.to(dev, non_blocking=True)
-        dgy = hgy.to(dev, non_blocking=True)
-        y = F.layer_forward(dx, t["theta"], t["pw"], t["pb"], t["postw"], t["postb"], None, None, **cfg)
-        F.layer_backward(dx, t["theta"], t["pw"], t["pb"], t["postw"], t["postb"], None, None, dgy,
-                         out=outs, **cfg)
-        if world > 1:
-            bucket.all_reduce()
-        hy.copy_(y, non_blocking=True)
-        hgx.copy_(gx, non_blocking=True)
-        hgrads.copy_(bucket.flat, non_blocking=True)
+        # public host-buffer API: chunked copy-in / kernels / copy-out pipeline on three streams
+        pipe.step(hx, hgy, dev_params, hy, hgx, hgrads)
 
     for _ in range(2 if e2e_steps else 0):
         e2e_step()
@@ -382,6 +379,7 @@ def main():
     ap.add_argument("--ref-rows", type=int, default=256, help="rows per step of --impl reference")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    ap.add_argument("--e2e-chunks", type=int, default=4, help="row chunks of the host-buffer pipeline")
     ap.add_argument("--batch", type=int, default=B_PER_GPU,
                     help="rows per GPU; anything but the default is a profiling-size run, not the benchmark")
     args = ap.parse_args()

@@ -1,0 +1,94 @@
+"""Forward + backward of one layer for callers whose activations live in host memory.
+
+The reference keeps everything in torch tensors and leaves host/device movement to the
+user (``QKAN.train_`` simply calls ``.to(self.device)`` per batch, ``src/qkan/qkan.py:1794-1795``).
+For batches that arrive in (pinned) host memory this helper hides the PCIe transfers behind the
+kernels: the batch is cut into row chunks, and three streams run as a pipeline —
+
+    copy-in   : x, grad_y of chunk k+1   host -> device
+    compute   : forward, backward of chunk k   (the C-ABI kernels)
+    copy-out  : y, grad_x of chunk k-1   device -> host
+
+Rows are independent, so chunking changes nothing but the order in which the batch-summed
+parameter gradients are accumulated (chunk partial sums are added in chunk order: still
+run-to-run reproducible).
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import torch
+
+from . import functional as qf
+from .parallel import GradBucket, layer_grad_shapes
+
+
+class HostLayerPipeline:
+    """Chunked, stream-overlapped ``y, grad_x, parameter gradients`` from host-resident ``x, grad_y``."""
+
+    def __init__(self, batch: int, in_dim: int, out_dim: int, reps: int, device, *, n_chunks: int = 4,
+                 dtype: torch.dtype = torch.float32, preact_trainable: bool = True,
+                 fast_measure: bool = True, use_postact_bias: bool = True, ansatz: str = "pz_encoding"):
+        self.device = torch.device(device)
+        self.cfg = dict(preact_trainable=preact_trainable, fast_measure=fast_measure,
+                        use_postact_bias=use_postact_bias, ansatz=ansatz)
+        n_chunks = max(1, min(n_chunks, batch))
+        step = (batch + n_chunks - 1) // n_chunks
+        self.spans = [(b, min(batch, b + step)) for b in range(0, batch, step)]
+        dev = self.device
+        self.dx = [torch.empty((e - b, in_dim), dtype=dtype, device=dev) for b, e in self.spans]
+        self.dgy = [torch.empty((e - b, out_dim), dtype=dtype, device=dev) for b, e in self.spans]
+        self.dgx = [torch.empty((e - b, in_dim), dtype=dtype, device=dev) for b, e in self.spans]
+        shapes = layer_grad_shapes(in_dim, out_dim, reps, preact_trainable=preact_trainable,
+                                   postact_bias=use_postact_bias)
+        if ansatz in ("rpz_encoding", "rpz"):
+            shapes["theta"] = (out_dim, in_dim, reps + 1, 1)
+        elif ansatz == "real":
+            shapes["theta"] = (out_dim, in_dim, reps, 1)
+        self.bucket = GradBucket(shapes, dev)                      # the summed gradients
+        self.chunk_buckets = [GradBucket(shapes, dev) for _ in self.spans]
+        self.s_in = torch.cuda.Stream(dev)
+        self.s_out = torch.cuda.Stream(dev)
+        self.ev_in = [torch.cuda.Event() for _ in self.spans]
+        self.ev_done = [torch.cuda.Event() for _ in self.spans]
+        self.ev_free = [torch.cuda.Event() for _ in self.spans]    # chunk buffers drained by copy-out
+        self._first = True
+
+    def step(self, hx: torch.Tensor, hgy: torch.Tensor, params: Dict[str, Optional[torch.Tensor]],
+             hy: torch.Tensor, hgx: torch.Tensor, hgrads: Optional[torch.Tensor] = None) -> GradBucket:
+        """Queue one forward+backward. ``hx, hgy, hy, hgx, hgrads`` are pinned host tensors; ``params`` holds the
+        device tensors theta, pw, pb, postw, postb (basew / mask optional). Returns the gradient bucket; the
+        caller synchronises (``torch.cuda.synchronize()`` or an event on the current stream) before reading."""
+        compute = torch.cuda.current_stream(self.device)
+        p = params
+        for k, (b, e) in enumerate(self.spans):
+            with torch.cuda.stream(self.s_in):
+                if not self._first:
+                    self.s_in.wait_event(self.ev_free[k])  # previous step finished reading this chunk's buffers
+                self.dx[k].copy_(hx[b:e], non_blocking=True)
+                self.dgy[k].copy_(hgy[b:e], non_blocking=True)
+                self.ev_in[k].record(self.s_in)
+            compute.wait_event(self.ev_in[k])
+            y = qf.layer_forward(self.dx[k], p["theta"], p["pw"], p["pb"], p["postw"], p.get("postb"),
+                                 p.get("basew"), p.get("mask"), **self.cfg)
+            outs = dict(self.chunk_buckets[k].views, x=self.dgx[k])
+            qf.layer_backward(self.dx[k], p["theta"], p["pw"], p["pb"], p["postw"], p.get("postb"),
+                              p.get("basew"), p.get("mask"), self.dgy[k], out=outs,
+                              want=tuple(outs), **self.cfg)
+            self.ev_done[k].record(compute)
+            with torch.cuda.stream(self.s_out):
+                self.s_out.wait_event(self.ev_done[k])
+                hy[b:e].copy_(y, non_blocking=True)
+                hgx[b:e].copy_(self.dgx[k], non_blocking=True)
+                self.ev_free[k].record(self.s_out)
+            y.record_stream(self.s_out)
+        self._first = False
+        flat = self.bucket.flat
+        flat.copy_(self.chunk_buckets[0].flat)
+        for cb in self.chunk_buckets[1:]:
+            flat.add_(cb.flat)
+        self.bucket.all_reduce()
+        if hgrads is not None:
+            hgrads.copy_(flat, non_blocking=True)
+        compute.wait_stream(self.s_out)
+        return self.bucket

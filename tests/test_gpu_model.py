@@ -130,3 +130,28 @@ def test_mlp_with_bf16_activations_and_sequence_axis():
     y.float().sum().backward()
     assert all(p.grad is not None and p.grad.dtype == torch.bfloat16
                for p in model.parameters() if p.requires_grad)
+
+
+def test_host_pipeline_matches_the_direct_call():
+    """Chunked, stream-overlapped host-buffer step == one direct call on device-resident tensors."""
+    from qkan_b200 import functional as F
+    from qkan_b200.host import HostLayerPipeline
+    from tests.util import random_problem
+
+    B, I, O, R = 1000, 70, 40, 3
+    p = random_problem(11, B, I, O, R, use_pb=True)
+    dev = {k: torch.from_numpy(v).cuda() for k, v in p.items() if v is not None}
+    cfg = dict(preact_trainable=True, fast_measure=True, use_postact_bias=True)
+    y_ref = F.layer_forward(dev["x"], dev["theta"], dev["pw"], dev["pb"], dev["postw"], dev["postb"], None, None, **cfg)
+    g_ref = F.layer_backward(dev["x"], dev["theta"], dev["pw"], dev["pb"], dev["postw"], dev["postb"], None, None,
+                             dev["gy"], **cfg)
+    pipe = HostLayerPipeline(B, I, O, R, "cuda:0", n_chunks=3)
+    hx, hgy = torch.from_numpy(p["x"]).pin_memory(), torch.from_numpy(p["gy"]).pin_memory()
+    hy, hgx = torch.empty(B, O).pin_memory(), torch.empty(B, I).pin_memory()
+    for _ in range(2):  # the second step reuses the chunk buffers of the first
+        bucket = pipe.step(hx, hgy, dev, hy, hgx)
+        torch.cuda.synchronize()
+        assert nerr(hy.numpy(), y_ref.cpu().numpy()) <= 1e-6
+        assert nerr(hgx.numpy(), g_ref["x"].cpu().numpy()) <= 1e-6
+        for name in ("theta", "preacts_weight", "preacts_bias", "postact_weights", "postact_bias"):
+            assert nerr(bucket[name].cpu().numpy(), g_ref[name].cpu().numpy()) <= 2e-6, name
