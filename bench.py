@@ -264,12 +264,15 @@ def run_b200(args):
             bwd_ev[k][1].record()
             if world > 1:
                 bucket.all_reduce()
-            ev[k][1].record()
+            ev[k][1].record()  # the step ends when the all-reduced gradients are there
         sync_all()
         wall = time.perf_counter() - wall0
     total_ms = sum(a.elapsed_time(b) for a, b in ev)
     fwd_ms = sum(a.elapsed_time(b) for a, b in fwd_ev) / args.steps
     bwd_ms = sum(a.elapsed_time(b) for a, b in bwd_ev) / args.steps
+    # gradient exchange as seen by this rank: from the end of its backward to the end of the all-reduce
+    # (the collective itself plus the wait for the slowest rank)
+    exchange_ms = sum(b[1].elapsed_time(e[1]) for b, e in zip(bwd_ev, ev)) / args.steps
     if world > 1:
         tt = torch.tensor([total_ms], device=dev, dtype=torch.float64)
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
@@ -357,6 +360,7 @@ def run_b200(args):
             "roofline": roofline, "cpu_baseline": cpu,
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
+            "gradient_exchange_ms": exchange_ms if world > 1 else 0.0,
             "gpu_launches": 7 * args.steps,
             "clocks": clk,
             "wall_s_timed_region": wall,
