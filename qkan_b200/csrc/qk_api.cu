@@ -52,7 +52,7 @@ Layout forward_layout(const QkDesc& d) {
     Layout l{};
     l.ipad = qk::round_up(d.in_dim, 32);
     l.table_off = 0;
-    size_t table = (size_t)d.out_dim * qk::table_rows(qk::compiled_reps(d.ansatz, d.reps)) * l.ipad * sizeof(float);
+    size_t table = (size_t)d.out_dim * qk::table_stride(qk::compiled_reps(d.ansatz, d.reps)) * l.ipad * sizeof(float);
     l.bias_off = qk::align256(table);
     l.total = l.bias_off + qk::align256((size_t)d.out_dim * sizeof(float));
     return l;

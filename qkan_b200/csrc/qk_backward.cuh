@@ -115,7 +115,7 @@ __global__ void __launch_bounds__(256) backward_kernel(BwdArgs a) {
     const int b0 = bt * tb;
     const int i0 = blockIdx.y * kWarp;
     const int i = i0 + lane;
-    const int K = table_rows(R);
+    constexpr int KS = table_stride(R);
     const IO* __restrict__ x = static_cast<const IO*>(a.x);
     const IO* __restrict__ gsrc = static_cast<const IO*>(EDGES ? a.gpostacts : a.gy);
     const int row0 = grp * rpg;
@@ -147,12 +147,9 @@ __global__ void __launch_bounds__(256) backward_kernel(BwdArgs a) {
         }
         for (int ol = 0; ol < nch; ++ol) {
             const int o = oc + ol;
-            const float* t = a.table + (size_t)o * K * a.ipad + i;
             EdgeFwd<R> e;
-            e.load(t, a.ipad);
-            e.load_bwd_extra(t, a.ipad);
-            float bw = 0.f;
-            if (BASE) bw = t[(size_t)t_bw(R) * a.ipad];
+            e.load(a.table + ((size_t)o * a.ipad + i) * KS);
+            const float bw = e.bw;
             float acc[NACC];
 #pragma unroll
             for (int k = 0; k < NACC; ++k) acc[k] = 0.f;

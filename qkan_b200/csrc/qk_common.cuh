@@ -41,7 +41,8 @@ __host__ __device__ constexpr int compiled_reps(int ansatz, int reps) {
 }
 
 // ---- per-edge constant table -------------------------------------------------
-// table[(o * K + k) * ipad + i], float32, ipad = in_dim rounded up to 32.
+// table[((o * ipad) + i) * KS + k], float32: the KS = table_stride(R) constants of one edge are
+// contiguous (a multiple of four floats, read as 128-bit loads), ipad = in_dim rounded up to 32.
 __host__ __device__ constexpr int t_vx0() { return 0; }
 __host__ __device__ constexpr int t_vy0() { return 1; }
 __host__ __device__ constexpr int t_vz0() { return 2; }
@@ -56,6 +57,7 @@ __host__ __device__ constexpr int t_ca0(int R) { return 4 * R + 4; }  // cos/sin
 __host__ __device__ constexpr int t_sa0(int R) { return 4 * R + 5; }
 __host__ __device__ constexpr int t_bw(int R) { return 4 * R + 6; }  // base_weight * mask
 __host__ __device__ constexpr int table_rows(int R) { return 4 * R + 7; }
+__host__ __device__ constexpr int table_stride(int R) { return (table_rows(R) + 3) / 4 * 4; }
 
 // accumulators of the backward, per edge, summed over the batch
 //   [0,R]      d/d theta[l,1]              (l = R is the final Ry)
@@ -162,34 +164,50 @@ __device__ __forceinline__ float qk_sqrt(float a) {
 }
 
 // ---- per-edge constants in registers -----------------------------------------
+// 128-bit loads of one edge's KS contiguous constants into registers
+template <int KS>
+__device__ __forceinline__ void load_edge_row(const float* __restrict__ t, float (&v)[KS]) {
+    const float4* __restrict__ t4 = reinterpret_cast<const float4*>(t);
+#pragma unroll
+    for (int q = 0; q < KS / 4; ++q) {
+        const float4 f = __ldg(t4 + q);
+        v[4 * q + 0] = f.x;
+        v[4 * q + 1] = f.y;
+        v[4 * q + 2] = f.z;
+        v[4 * q + 3] = f.w;
+    }
+}
+
 template <int R>
 struct EdgeFwd {
     float vx0, vy0, vz0;
     float pw[R], c[R];
-    float ca[R], sa[R];  // index 0 unused in the forward
-    float cf, sf, w;
+    float ca[R], sa[R];  // index 0 is used by the backward only
+    float cf, sf, w, bw;
 
-    __device__ __forceinline__ void load(const float* __restrict__ t, int stride) {
-        vx0 = t[t_vx0() * stride];
-        vy0 = t[t_vy0() * stride];
-        vz0 = t[t_vz0() * stride];
+    // t points at this edge's row of the table
+    __device__ __forceinline__ void load(const float* __restrict__ t) {
+        float v[table_stride(R)];
+        load_edge_row(t, v);
+        vx0 = v[t_vx0()];
+        vy0 = v[t_vy0()];
+        vz0 = v[t_vz0()];
 #pragma unroll
         for (int l = 0; l < R; ++l) {
-            pw[l] = t[t_pw(l) * stride];
-            c[l] = t[t_c(l) * stride];
+            pw[l] = v[t_pw(l)];
+            c[l] = v[t_c(l)];
         }
 #pragma unroll
         for (int l = 1; l < R; ++l) {
-            ca[l] = t[t_ca(R, l) * stride];
-            sa[l] = t[t_sa(R, l) * stride];
+            ca[l] = v[t_ca(R, l)];
+            sa[l] = v[t_sa(R, l)];
         }
-        cf = t[t_cf(R) * stride];
-        sf = t[t_sf(R) * stride];
-        w = t[t_w(R) * stride];
-    }
-    __device__ __forceinline__ void load_bwd_extra(const float* __restrict__ t, int stride) {
-        ca[0] = t[t_ca0(R) * stride];
-        sa[0] = t[t_sa0(R) * stride];
+        ca[0] = v[t_ca0(R)];
+        sa[0] = v[t_sa0(R)];
+        cf = v[t_cf(R)];
+        sf = v[t_sf(R)];
+        w = v[t_w(R)];
+        bw = v[t_bw(R)];
     }
 };
 
@@ -199,13 +217,15 @@ struct EdgeFwd {
 // cos(alpha) rsqrt(1 + |sin(alpha)|) (fast). Table rows: 0 = A, 1 = C reduced to [-pi,pi], 3 = weight.
 template <>
 struct EdgeFwd<0> {
-    float a, c, w;
-    __device__ __forceinline__ void load(const float* __restrict__ t, int stride) {
-        a = t[0];
-        c = t[stride];
-        w = t[t_w(0) * stride];
+    float a, c, w, bw;
+    __device__ __forceinline__ void load(const float* __restrict__ t) {
+        float v[table_stride(0)];
+        load_edge_row(t, v);
+        a = v[0];
+        c = v[1];
+        w = v[t_w(0)];
+        bw = v[t_bw(0)];
     }
-    __device__ __forceinline__ void load_bwd_extra(const float*, int) {}
 };
 
 template <bool FAST, bool PRECISE>

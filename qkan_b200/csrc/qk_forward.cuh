@@ -46,7 +46,7 @@ __global__ void __launch_bounds__(512) forward_kernel(FwdArgs a) {
     const int ot_eff = min(ot, a.out_dim - o0);
     const int warp = threadIdx.x / kWarp, lane = threadIdx.x % kWarp;
     const int nwarps = blockDim.x / kWarp;
-    const int K = table_rows(R);
+    constexpr int KS = table_stride(R);
     const IO* __restrict__ x = static_cast<const IO*>(a.x);
 
     if (!EDGES)
@@ -70,11 +70,9 @@ __global__ void __launch_bounds__(512) forward_kernel(FwdArgs a) {
             for (int sub = 0; sub < nsub; ++sub) {
                 const int col = sub * kWarp + lane;
                 const int i = ic0 + col;
-                const float* t = a.table + (size_t)o * K * a.ipad + i;
                 EdgeFwd<R> e;
-                e.load(t, a.ipad);
-                float bw = 0.f;
-                if (BASE) bw = t[(size_t)t_bw(R) * a.ipad];
+                e.load(a.table + ((size_t)o * a.ipad + i) * KS);
+                const float bw = e.bw;
                 for (int rg = 0; rg < tb; rg += 32) {
                     float v[32];
 #pragma unroll

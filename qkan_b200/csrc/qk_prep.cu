@@ -13,9 +13,9 @@ __global__ void prep_table_kernel(PrepArgs a) {
     const int o = blockIdx.y;
     if (i >= a.ipad) return;
     const int R = a.reps, RK = a.rk;
-    const int K = table_rows(RK);
-    float* t = a.table + (size_t)o * K * a.ipad + i;
-    auto put = [&](int row, float v) { t[(size_t)row * a.ipad] = v; };
+    const int K = table_stride(RK);
+    float* t = a.table + ((size_t)o * a.ipad + i) * K;
+    auto put = [&](int row, float v) { t[row] = v; };
     if (i >= a.in_dim) {
         for (int k = 0; k < K; ++k) put(k, 0.f);
         return;
