@@ -42,6 +42,16 @@ int check_desc(const QkDesc* d) {
     return QK_OK;
 }
 
+// Forward with frozen preacts of the pz circuit: data angles are x + const and are evaluated by angle
+// addition from (cos x, sin x) staged once per tile. Not combined with QK_PRECISE_MATH or with padded
+// (> 8) circuits. (The same form was measured for the backward and was 3-5 % slower there: the backward is
+// bound by issue slots, not by the special-function unit, so it keeps the generic kernel.)
+bool use_xtrig(const QkDesc& d) {
+    const int rk = qk::compiled_reps(d.ansatz, d.reps);
+    return d.ansatz == QK_ANSATZ_PZ && !(d.flags & QK_PREACT_TRAINABLE) && !(d.flags & QK_PRECISE_MATH) &&
+           rk >= 1 && rk <= 8 && !getenv("QK_NO_XTRIG");
+}
+
 struct Layout {
     int ipad;
     size_t table_off, bias_off, colsum_off, partials_off, total;
@@ -121,6 +131,8 @@ int run_forward(const QkDesc* desc, const void* x, const float* theta, const flo
     p.mask = edges ? nullptr : mask;
     p.table = reinterpret_cast<float*>(wsb + l.table_off);
     p.bias = edges ? nullptr : reinterpret_cast<float*>(wsb + l.bias_off);
+    const bool xtrig = use_xtrig(d);
+    p.xtrig = xtrig;
     cudaError_t e = qk::launch_prep(p, st);
     if (e != cudaSuccess) return cuda_fail(e, "prep launch");
 
@@ -130,7 +142,8 @@ int run_forward(const QkDesc* desc, const void* x, const float* theta, const flo
     f.out_dim = d.out_dim;
     f.ipad = l.ipad;
     f.precise = (d.flags & QK_PRECISE_MATH) != 0;
-    f.cfg = qk::choose_fwd_cfg(d, edges, has_base);
+    f.xtrig = xtrig;
+    f.cfg = qk::choose_fwd_cfg(d, edges, has_base, xtrig);
     if (getenv("QK_DEBUG"))
         fprintf(stderr, "[qk] forward B=%d I=%d O=%d R=%d: tile %d rows x %d outputs, grid %d x %d, smem %zu\n",
                 d.batch, d.in_dim, d.out_dim, d.reps, f.cfg.tb, f.cfg.ot, f.cfg.grid_b, f.cfg.grid_o, f.cfg.smem);
@@ -198,6 +211,7 @@ int run_backward(const QkDesc* desc, const void* x, const float* theta, const fl
     p.mask = edges ? nullptr : mask;
     p.table = reinterpret_cast<float*>(wsb + l.table_off);
     p.bias = nullptr;
+    p.xtrig = 0;
     cudaError_t e = qk::launch_prep(p, st);
     if (e != cudaSuccess) return cuda_fail(e, "prep launch");
 

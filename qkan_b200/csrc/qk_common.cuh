@@ -286,4 +286,37 @@ __device__ __forceinline__ float edge_forward(const EdgeFwd<R>& e, float x, floa
     }
 }
 
+// Forward for frozen preacts (the data angle is x + c_l): sin/cos of x are taken once per (row, column)
+// when the tile is staged, and every data gate gets its angle by the addition formulas from the
+// per-edge constants (cos c_l, sin c_l) that the table holds in place of (pw_l, c_l) in this mode.
+// No special-function call is left in the loop except the readout.
+template <int R, bool FAST>
+__device__ __forceinline__ float edge_forward_xtrig(const EdgeFwd<R>& e, float cx, float sx) {
+    float vx = e.vx0, vy = e.vy0, vz = e.vz0;
+#pragma unroll
+    for (int l = 0; l < R; ++l) {
+        if (l > 0) {  // Ry(theta[l,1])
+            float nx = fmaf(vz, e.sa[l], vx * e.ca[l]);
+            float nz = fmaf(-vx, e.sa[l], vz * e.ca[l]);
+            vx = nx;
+            vz = nz;
+        }
+        const float c = fmaf(-sx, e.c[l], cx * e.pw[l]);  // cos(x + c_l)
+        const float s = fmaf(cx, e.c[l], sx * e.pw[l]);   // sin(x + c_l)
+        float nx = fmaf(-vy, s, vx * c);
+        float ny = fmaf(vx, s, vy * c);
+        vx = nx;
+        vy = ny;
+    }
+    {
+        float nx = fmaf(vz, e.sf, vx * e.cf);
+        float nz = fmaf(-vx, e.sf, vz * e.cf);
+        vx = nx;
+        vz = nz;
+    }
+    if (!FAST) return vz;
+    const float s2 = fmaf(vx, vx, vy * vy);
+    return vz * qk_rsqrt<false>(1.0f + qk_sqrt<false>(s2));
+}
+
 }  // namespace qk

@@ -32,7 +32,7 @@ constexpr size_t kSmemPerSm = 227 * 1024;
 // Tile shapes are chosen with a small cost model: the busiest SM gets ceil(CTAs / 148) CTAs, a
 // CTA's time grows with the edges x rows it owns plus its per-edge set-up, and too few resident
 // warps cannot keep the issue slots busy. The largest tile wins ties (fewest partials / re-reads).
-FwdCfg choose_fwd_cfg(const QkDesc& d, bool edges, bool base) {
+FwdCfg choose_fwd_cfg(const QkDesc& d, bool edges, bool base, bool xtrig) {
     const int ipad = round_up(d.in_dim, 32);
     FwdCfg best{};
     double best_cost = -1.0;
@@ -46,7 +46,8 @@ FwdCfg choose_fwd_cfg(const QkDesc& d, bool edges, bool base) {
             if (c.ot < 16 && c.ot < d.out_dim) continue;  // fewer outputs than warps: idle warps
             c.grid_b = (d.batch + tb - 1) / tb;
             c.grid_o = (d.out_dim + c.ot - 1) / c.ot;
-            c.smem = (size_t)tb * c.ich * 4 * (base ? 2 : 1) + (edges ? 0 : (size_t)c.ot * (tb + 1) * 4);
+            c.smem = (size_t)tb * c.ich * 4 * ((xtrig ? 2 : 1) + (base ? 1 : 0)) +
+                     (edges ? 0 : (size_t)c.ot * (tb + 1) * 4);
             if (c.smem > 200 * 1024) continue;
             const long ctas = (long)c.grid_b * c.grid_o;
             const long per_sm = (ctas + kSmCount - 1) / kSmCount;  // one CTA of 16 warps per SM at a time

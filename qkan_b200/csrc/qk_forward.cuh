@@ -33,13 +33,16 @@ __device__ __forceinline__ float transpose_reduce32(float (&v)[32], int lane) {
 
 __device__ __forceinline__ float silu_f(float v) { return v / (1.f + expf(-v)); }
 
-template <int R, bool FAST, typename IO, bool BASE, bool EDGES, bool PRECISE>
+// XTRIG: the x tile holds (cos x, sin x) pairs and the data gates use the angle-addition form
+// (frozen preacts, see edge_forward_xtrig).
+template <int R, bool FAST, typename IO, bool BASE, bool EDGES, bool PRECISE, bool XTRIG>
 __global__ void __launch_bounds__(512) forward_kernel(FwdArgs a) {
     extern __shared__ __align__(16) float smem[];
     const int tb = a.cfg.tb, ot = a.cfg.ot, ich = a.cfg.ich;
     const int ldy = tb + 1;
-    float* x_s = smem;                           // [tb][ich]
-    float* y_s = x_s + (size_t)tb * ich;         // [ot][tb+1]
+    constexpr int XW = XTRIG ? 2 : 1;            // floats per staged x element
+    float* x_s = smem;                           // [tb][ich] (x) or [tb][ich][2] (cos x, sin x)
+    float* y_s = x_s + (size_t)tb * ich * XW;    // [ot][tb+1]
     float* b_s = y_s + (EDGES ? 0 : (size_t)ot * ldy);  // [tb][ich] silu(x), BASE only
     const int b0 = blockIdx.x * tb;
     const int o0 = blockIdx.y * ot;
@@ -60,7 +63,13 @@ __global__ void __launch_bounds__(512) forward_kernel(FwdArgs a) {
             float v = 0.f;
             if (b0 + r < a.batch && ic0 + c < a.in_dim)
                 v = ld_as_float(x + (size_t)(b0 + r) * a.in_dim + ic0 + c);
-            x_s[r * ich + c] = v;
+            if (XTRIG) {
+                float sx, cx;
+                precise_sincos(v, sx, cx);
+                reinterpret_cast<float2*>(x_s)[r * ich + c] = make_float2(cx, sx);
+            } else {
+                x_s[r * ich + c] = v;
+            }
             if (BASE) b_s[r * ich + c] = silu_f(v);
         }
         __syncthreads();
@@ -77,10 +86,15 @@ __global__ void __launch_bounds__(512) forward_kernel(FwdArgs a) {
                     float v[32];
 #pragma unroll
                     for (int r = 0; r < 32; ++r) {
-                        float xv = x_s[(rg + r) * ich + col];
-                        float vx, vy, vz, ir, rr;
-                        float p = edge_forward<R, FAST, false, PRECISE>(e, xv, nullptr, nullptr, vx, vy, vz,
-                                                               ir, rr);
+                        float p;
+                        if constexpr (XTRIG) {
+                            const float2 t = reinterpret_cast<const float2*>(x_s)[(rg + r) * ich + col];
+                            p = edge_forward_xtrig<R, FAST>(e, t.x, t.y);
+                        } else {
+                            float xv = x_s[(rg + r) * ich + col];
+                            float vx, vy, vz, ir, rr;
+                            p = edge_forward<R, FAST, false, PRECISE>(e, xv, nullptr, nullptr, vx, vy, vz, ir, rr);
+                        }
                         if (EDGES) {
                             v[r] = p;
                         } else {
@@ -119,9 +133,12 @@ __global__ void __launch_bounds__(512) forward_kernel(FwdArgs a) {
 
 template <int R, bool FAST, typename IO, bool BASE, bool EDGES>
 static cudaError_t launch_fwd_t(const FwdArgs& a, cudaStream_t st) {
-    auto kern = forward_kernel<R, FAST, IO, BASE, EDGES, false>;
+    auto kern = forward_kernel<R, FAST, IO, BASE, EDGES, false, false>;
     if constexpr (std::is_same<IO, float>::value) {  // the full-precision variant exists for float32 I/O
-        if (a.precise) kern = forward_kernel<R, FAST, IO, BASE, EDGES, true>;
+        if (a.precise) kern = forward_kernel<R, FAST, IO, BASE, EDGES, true, false>;
+    }
+    if constexpr (R >= 1 && R <= 8) {  // frozen-preact form (no identity padding possible beyond 8)
+        if (a.xtrig) kern = forward_kernel<R, FAST, IO, BASE, EDGES, false, true>;
     }
     cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            (int)a.cfg.smem);

@@ -9,6 +9,7 @@ struct PrepArgs {
     int in_dim, out_dim, reps, ipad;
     int rk;      // compiled_reps(ansatz, reps): the table is laid out for this repetition count
     int ansatz;  // QkAnsatz
+    int xtrig;   // frozen-preact forward: rows (pw_l, c_l) hold (cos c_l, sin c_l) instead
     unsigned flags;
     int param_dtype;
     const float* theta;
@@ -61,6 +62,7 @@ struct BwdCfg {
 struct FwdArgs {
     int batch, in_dim, out_dim, ipad;
     int precise;  // QK_PRECISE_MATH requested (honoured for float32 I/O)
+    int xtrig;    // use the frozen-preact kernel (table built with PrepArgs.xtrig)
     FwdCfg cfg;
     const void* x;
     const float* table;
@@ -81,7 +83,7 @@ struct BwdArgs {
     float* partials;
 };
 
-FwdCfg choose_fwd_cfg(const QkDesc& d, bool edges, bool base);
+FwdCfg choose_fwd_cfg(const QkDesc& d, bool edges, bool base, bool xtrig);
 BwdCfg choose_bwd_cfg(const QkDesc& d, bool base);
 
 cudaError_t launch_prep(const PrepArgs& a, cudaStream_t st);

@@ -59,7 +59,12 @@ __global__ void prep_table_kernel(PrepArgs a) {
     put(t_ca0(RK), ca0);
     put(t_sa0(RK), sa0);
     for (int l = 0; l < RK; ++l) {
-        if (l < R) {
+        if (l < R && a.xtrig) {  // frozen preacts, angle x + c_l: the forward wants cos/sin of c_l
+            float s, c;
+            sincosf(th_rz(l + 1), &s, &c);
+            put(t_pw(l), c);
+            put(t_c(l), s);
+        } else if (l < R) {
             put(t_pw(l), ptr ? a.pw[e * R + l] : 1.f);
             put(t_c(l), (ptr ? a.pb[e * R + l] : 0.f) + th_rz(l + 1));
         } else {  // identity padding
