@@ -331,6 +331,7 @@ def run_b200(args):
         roofline = {
             "bound": "fp32_issue", "achieved": achieved, "peak": peak_issue, "unit": "Tlane-op/s",
             "frac": achieved / peak_issue,
+            "roofline_ms": 1e3 * issue_roofline_seconds(edges_per_rank, REPS, "fwd_bwd"),
             "frac_at_sampled_clock": (achieved / (peak_issue * clk["sm_mhz"] / 1965.0)
                                       if clk.get("sm_mhz") else None),
             "peak_source": "148 SMs x 128 FP32 lanes x 1.965 GHz (issue roofline; SFU 16 lanes/SM)",

@@ -7,7 +7,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from ctypes import POINTER, Structure, c_char_p, c_int, c_int32, c_size_t, c_uint32, c_void_p
+from ctypes import Structure, c_char_p, c_int, c_int32, c_size_t, c_uint32, c_void_p
 
 QK_ABI_VERSION = 2
 
@@ -115,4 +115,3 @@ def desc_pointer(desc: QkDesc):
 
 __all__ = [name for name in dir() if name.startswith("QK") or name in (
     "QkDesc", "QkanLibraryError", "ANSATZ_CODES", "load", "last_error", "check", "desc_pointer", "SYMBOLS", "LIB_PATH")]
-_ = POINTER  # re-exported for callers that build their own argument blocks
