@@ -1,0 +1,86 @@
+"""CUDA-graph capture of whole-model inference and of one training step.
+
+Small layers are bound by launches rather than by arithmetic: a forward + backward of one QKAN
+layer is seven launches of this library plus the autograd bookkeeping around them. The reference
+offers the same two helpers for that regime (``src/qkan/inference.py:68-135, 205-330``); here
+they are thin wrappers over ``torch.cuda.CUDAGraph``, which works because the kernels launch on
+the current stream, never synchronise and take all their memory from the caller.
+"""
+from __future__ import annotations
+
+from typing import Callable
+
+import torch
+from torch import nn
+
+
+def _warm(fn: Callable[[], None], warmup: int) -> None:
+    """Run ``fn`` a few times on a side stream (allocations, lazy initialisation) before capture."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(max(warmup, 1)):
+            fn()
+    torch.cuda.current_stream().wait_stream(side)
+
+
+def make_graphed_inference(model: nn.Module, sample_input: torch.Tensor,
+                           warmup: int = 3) -> Callable[[torch.Tensor], torch.Tensor]:
+    """Capture ``model(sample_input)`` under ``no_grad``; the returned callable replays it for same-shaped inputs.
+
+    The result is a view of a static buffer that the next call overwrites: clone it to keep it.
+    """
+    static_x = sample_input.detach().clone()
+    with torch.no_grad():
+        _warm(lambda: model(static_x), warmup)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            static_y = model(static_x)
+
+    def replay(x: torch.Tensor) -> torch.Tensor:
+        if x.shape != static_x.shape or x.dtype != static_x.dtype:
+            raise ValueError(f"graph was captured for {tuple(static_x.shape)} {static_x.dtype}, "
+                             f"got {tuple(x.shape)} {x.dtype}")
+        static_x.copy_(x)
+        graph.replay()
+        return static_y
+
+    return replay
+
+
+def make_graphed_train_step(model: nn.Module, sample_input: torch.Tensor, sample_target: torch.Tensor,
+                            loss_fn: Callable[[torch.Tensor, torch.Tensor], torch.Tensor],
+                            optimizer: torch.optim.Optimizer,
+                            warmup: int = 3) -> Callable[[torch.Tensor, torch.Tensor], torch.Tensor]:
+    """Capture forward + loss + gradients; ``optimizer.step()`` stays with the caller.
+
+    After ``loss = step(x, y)`` every trainable parameter's ``.grad`` holds this step's gradient
+    (static buffers, overwritten by the next call) and ``loss`` is a static scalar tensor.
+    """
+    static_x = sample_input.detach().clone()
+    static_t = sample_target.detach().clone()
+    params = [p for p in model.parameters() if p.requires_grad]
+
+    # Gradients are taken with torch.autograd.grad, not .backward(): the accumulation nodes that
+    # .backward() runs are tied to the stream on which each parameter was first used (usually the
+    # default stream), and running them inside a capture on another stream is an error.
+    def grads_of(loss):
+        return torch.autograd.grad(loss, params, allow_unused=True)
+
+    _warm(lambda: grads_of(loss_fn(model(static_x), static_t)), warmup)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        static_loss = loss_fn(model(static_x), static_t)
+        static_grads = grads_of(static_loss)
+
+    def train_step(x: torch.Tensor, target: torch.Tensor) -> torch.Tensor:
+        if x.shape != static_x.shape or target.shape != static_t.shape:
+            raise ValueError("graph was captured for other input / target shapes")
+        static_x.copy_(x)
+        static_t.copy_(target)
+        graph.replay()
+        for p, g in zip(params, static_grads):  # re-attach: an optimizer.zero_grad() in between is harmless
+            p.grad = g
+        return static_loss
+
+    return train_step

@@ -155,3 +155,35 @@ def test_host_pipeline_matches_the_direct_call():
         assert nerr(hgx.numpy(), g_ref["x"].cpu().numpy()) <= 1e-6
         for name in ("theta", "preacts_weight", "preacts_bias", "postact_weights", "postact_bias"):
             assert nerr(bucket[name].cpu().numpy(), g_ref[name].cpu().numpy()) <= 2e-6, name
+
+
+def test_graphed_train_step_and_inference_match_eager():
+    """Whole-model CUDA-graph capture (the launch-bound regime): same gradients and outputs as eager."""
+    from qkan_b200.graph import make_graphed_inference, make_graphed_train_step
+
+    torch.manual_seed(0)
+    model = QKAN([20, 16, 4], reps=2, seed=3, preact_trainable=True, postact_weight_trainable=True).to("cuda")
+    x = torch.rand(64, 20, device="cuda") * 2 - 1
+    labels = torch.randint(0, 4, (64,), device="cuda")
+    loss_fn = torch.nn.functional.cross_entropy
+    opt = torch.optim.SGD(model.parameters(), lr=0.0)
+    loss_e = loss_fn(model(x), labels)
+    loss_e.backward()
+    eager = {n: p.grad.clone() for n, p in model.named_parameters() if p.grad is not None}
+    step = make_graphed_train_step(model, x, labels, loss_fn, opt)
+    for _ in range(2):  # replays are idempotent
+        loss_g = step(x, labels)
+        torch.cuda.synchronize()
+        assert abs(float(loss_g) - float(loss_e)) <= 1e-6 * abs(float(loss_e))
+        for n, p in model.named_parameters():
+            if n in eager:
+                assert nerr(p.grad.cpu().numpy(), eager[n].cpu().numpy()) <= 1e-6, n
+    model.eval()
+    with torch.no_grad():
+        y_e = model(x)
+    infer = make_graphed_inference(model, x)
+    x2 = torch.rand_like(x)
+    with torch.no_grad():
+        y2_e = model(x2)
+    assert nerr(infer(x).cpu().numpy(), y_e.cpu().numpy()) <= 1e-6
+    assert nerr(infer(x2).cpu().numpy(), y2_e.cpu().numpy()) <= 1e-6
