@@ -59,19 +59,24 @@ def make_graphed_train_step(model: nn.Module, sample_input: torch.Tensor, sample
     """
     static_x = sample_input.detach().clone()
     static_t = sample_target.detach().clone()
-    params = [p for p in model.parameters() if p.requires_grad]
+    named = [(n, p) for n, p in model.named_parameters() if p.requires_grad]
+    params = [p for _, p in named]
 
-    # Gradients are taken with torch.autograd.grad, not .backward(): the accumulation nodes that
-    # .backward() runs are tied to the stream on which each parameter was first used (usually the
-    # default stream), and running them inside a capture on another stream is an error.
-    def grads_of(loss):
-        return torch.autograd.grad(loss, params, allow_unused=True)
+    # The step is differentiated with respect to fresh leaf tensors that alias the parameters' storage
+    # (so optimizer updates stay visible to the replays), through torch.autograd.grad. Differentiating the
+    # parameters themselves would reuse their gradient-accumulation nodes, which stay tied to the stream of
+    # an earlier eager step for as long as any old autograd graph is alive, and running those inside a
+    # capture on another stream is an error (the reference re-allocates every parameter for this reason,
+    # src/qkan/inference.py:137-203).
+    def loss_and_grads():
+        leaves = {n: p.detach().requires_grad_(True) for n, p in named}
+        loss = loss_fn(torch.func.functional_call(model, leaves, (static_x,)), static_t)
+        return loss, torch.autograd.grad(loss, list(leaves.values()), allow_unused=True)
 
-    _warm(lambda: grads_of(loss_fn(model(static_x), static_t)), warmup)
+    _warm(loss_and_grads, warmup)
     graph = torch.cuda.CUDAGraph()
     with torch.cuda.graph(graph):
-        static_loss = loss_fn(model(static_x), static_t)
-        static_grads = grads_of(static_loss)
+        static_loss, static_grads = loss_and_grads()
 
     def train_step(x: torch.Tensor, target: torch.Tensor) -> torch.Tensor:
         if x.shape != static_x.shape or target.shape != static_t.shape:
