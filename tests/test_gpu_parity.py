@@ -144,3 +144,28 @@ def test_empty_batch_and_bad_arguments():
         F.layer_forward(torch.zeros((4, 5), device="cuda"), th, pw, pb, postw, **cfg)
     with pytest.raises(RuntimeError):
         F.layer_forward(torch.zeros((4, 3)), th, pw, pb, postw, **cfg)
+
+
+def test_c_abi_rejects_bad_workspaces_and_null_pointers():
+    """Error behaviour of the raw entry points: negative return code, text in qk_last_error, nothing launched."""
+    from qkan_b200 import _abi
+
+    lib = _abi.load()
+    desc = _abi.QkDesc(8, 4, 3, 2, _abi.QK_F32, _abi.QK_F32, _abi.QK_FAST_MEASURE, _abi.QK_ANSATZ_PZ)
+    dp = _abi.desc_pointer(desc)
+    need = lib.qk_forward_workspace_bytes(dp)
+    buf = torch.zeros(need + 512, dtype=torch.uint8, device="cuda")
+    t = torch.zeros(4096, device="cuda")
+    args = [t.data_ptr()] * 5 + [None, None, None, t.data_ptr()]  # x theta pw pb postw | postb basew mask | y
+    aligned = (buf.data_ptr() + 255) // 256 * 256
+    assert lib.qk_pz_forward(dp, *args, aligned, need - 1, None) == _abi.QK_ERR_WORKSPACE
+    assert b"workspace too small" in lib.qk_last_error()
+    assert lib.qk_pz_forward(dp, *args, aligned + 4, need, None) == _abi.QK_ERR_WORKSPACE
+    assert b"aligned" in lib.qk_last_error()
+    assert lib.qk_pz_forward(dp, None, *args[1:], aligned, need, None) == _abi.QK_ERR_BAD_ARGUMENT
+    bad = _abi.QkDesc(8, 4, 3, 17, _abi.QK_F32, _abi.QK_F32, 0, _abi.QK_ANSATZ_PZ)
+    assert lib.qk_pz_forward(_abi.desc_pointer(bad), *args, aligned, need, None) == _abi.QK_ERR_UNSUPPORTED
+    bad = _abi.QkDesc(8, 4, 3, 2, _abi.QK_F32, _abi.QK_F32, 0, 7)
+    assert lib.qk_pz_forward(_abi.desc_pointer(bad), *args, aligned, need, None) == _abi.QK_ERR_BAD_ARGUMENT
+    assert lib.qk_pz_forward(dp, *args, aligned, need, None) == _abi.QK_OK
+    torch.cuda.synchronize()
