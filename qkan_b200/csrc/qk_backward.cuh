@@ -23,9 +23,10 @@ namespace qk {
 
 __device__ __forceinline__ float sigmoid_f(float v) { return 1.f / (1.f + expf(-v)); }
 
+// Returns gx0 + d/dx of this edge (gx0 is the grad_x accumulated over the outputs walked so far).
 template <int R, bool FAST, bool BASE, bool EDGES, int NACC, bool PRECISE>
 __device__ __forceinline__ float edge_backward(const EdgeFwd<R>& e, float bw, float x, float g,
-                                               float sl, float dsl, float (&acc)[NACC]) {
+                                               float sl, float dsl, float gx0, float (&acc)[NACC]) {
     if constexpr (R == 0) {
         // "real" ansatz: p = f(alpha), alpha = A x + C. acc[0] = sum dL/dalpha, acc[1] = sum dL/dalpha * x
         float s, c, r = 1.f;
@@ -41,7 +42,7 @@ __device__ __forceinline__ float edge_backward(const EdgeFwd<R>& e, float bw, fl
         const float ga = gp * dp;
         acc[0] += ga;
         acc[1] = fmaf(ga, x, acc[1]);
-        float gx = ga * e.a;
+        float gx = fmaf(ga, e.a, gx0);
         if (BASE) {
             acc[a_bw(0)] = fmaf(g, sl, acc[a_bw(0)]);
             gx = fmaf(g * bw, dsl, gx);
@@ -55,10 +56,9 @@ __device__ __forceinline__ float edge_backward(const EdgeFwd<R>& e, float bw, fl
     // w = v x a, a = cotangent of the final Bloch vector (its z component of w is 0)
     float wx, wy, wz;
     if (FAST) {
-        // a = (q vx, q vy, az) with q = -gp r^3 vz / (2 rho); then v x a = (vy k, -vx k, 0), k = az - vz q
-        const float az = gp * r;
-        const float t = az * (r * r);
-        const float k = fmaf((0.5f * vz) * vz, t * inv_rho, az);
+        // a = (q vx, q vy, az), az = gp r, q = -gp r^3 vz / (2 rho); then v x a = (vy k, -vx k, 0), k = az - vz q
+        // with p = vz r:  k = gp r (1 + p^2 / (2 rho))
+        const float k = (gp * r) * fmaf((0.5f * p) * p, inv_rho, 1.0f);
         wx = vy * k;
         wy = -(vx * k);
     } else {
@@ -68,7 +68,7 @@ __device__ __forceinline__ float edge_backward(const EdgeFwd<R>& e, float bw, fl
     acc[a_ry(R)] += wy;  // final Ry(theta[R,1])
     wz = wx * e.sf;
     wx = wx * e.cf;
-    float gx = 0.f;
+    float gx = gx0;
 #pragma unroll
     for (int l = R - 1; l >= 0; --l) {
         // merged Rz(pw_l x + c_l): its angle gradient is wz
@@ -137,11 +137,30 @@ __global__ void __launch_bounds__(256) backward_kernel(BwdArgs a) {
         const int nch = min(kGyChunk, a.out_dim - oc);
         if (!EDGES) {
             // stage grad_y[b0 .. b0+tb, oc .. oc+nch) transposed; rows past the batch read as 0
-            for (int idx = threadIdx.x; idx < tb * kGyChunk; idx += blockDim.x) {
-                const int r = idx / kGyChunk, c = idx % kGyChunk;
-                float v = 0.f;
-                if (b0 + r < a.batch && c < nch) v = ld_as_float(gsrc + (size_t)(b0 + r) * a.out_dim + oc + c);
-                gy_s[c * tb + r] = v;
+            if (std::is_same<IO, float>::value && nch == kGyChunk && (a.out_dim & 3) == 0 &&
+                (reinterpret_cast<uintptr_t>(gsrc) & 15) == 0) {
+                // full chunk of float32 rows from a 16-byte aligned grad_y: two 128-bit loads per row
+                // (oc and out_dim are multiples of 4, so every row segment is aligned too)
+                for (int idx = threadIdx.x; idx < tb * 2; idx += blockDim.x) {
+                    const int r = idx >> 1, h = idx & 1;
+                    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (b0 + r < a.batch)
+                        v = __ldg(reinterpret_cast<const float4*>(
+                            reinterpret_cast<const float*>(gsrc) + (size_t)(b0 + r) * a.out_dim + oc + 4 * h));
+                    float* dst = gy_s + (4 * h) * tb + r;
+                    dst[0] = v.x;
+                    dst[tb] = v.y;
+                    dst[2 * tb] = v.z;
+                    dst[3 * tb] = v.w;
+                }
+            } else {
+                for (int idx = threadIdx.x; idx < tb * kGyChunk; idx += blockDim.x) {
+                    const int r = idx / kGyChunk, c = idx % kGyChunk;
+                    float v = 0.f;
+                    if (b0 + r < a.batch && c < nch)
+                        v = ld_as_float(gsrc + (size_t)(b0 + r) * a.out_dim + oc + c);
+                    gy_s[c * tb + r] = v;
+                }
             }
             __syncthreads();
         }
@@ -195,9 +214,8 @@ __global__ void __launch_bounds__(256) backward_kernel(BwdArgs a) {
                 }
 #pragma unroll
                 for (int u = 0; u < RU; ++u) {
-                    float gx = edge_backward<R, FAST, BASE, EDGES, NACC, PRECISE>(e, bw, xv[u], g[u], sl[u],
-                                                                         dsl[u], acc);
-                    p[u * ROW + 1] = gxo[u] + gx;
+                    p[u * ROW + 1] = edge_backward<R, FAST, BASE, EDGES, NACC, PRECISE>(e, bw, xv[u], g[u], sl[u],
+                                                                                     dsl[u], gxo[u], acc);
                 }
             }
 
@@ -206,11 +224,13 @@ __global__ void __launch_bounds__(256) backward_kernel(BwdArgs a) {
 #pragma unroll
             for (int k = 0; k < NACC; ++k) red[(grp * NACC + k) * 32 + lane] = acc[k];
             __syncthreads();
-            for (int idx = threadIdx.x; idx < NACC * 32; idx += blockDim.x) {
-                const int k = idx / 32, l = idx % 32;
+            // warp `grp` sums accumulators grp, grp + groups, ... over the groups (fixed order) for its 32 columns
+            float* const part = a.partials + ((size_t)bt * a.out_dim + o) * NACC * a.ipad + i0 + lane;
+            for (int k = grp; k < NACC; k += groups) {
+                const float* r = red + k * 32 + lane;
                 float s = 0.f;
-                for (int gi = 0; gi < groups; ++gi) s += red[(gi * NACC + k) * 32 + l];
-                a.partials[(((size_t)bt * a.out_dim + o) * NACC + k) * a.ipad + i0 + l] = s;
+                for (int gi = 0; gi < groups; ++gi) s += r[gi * NACC * 32];
+                part[(size_t)k * a.ipad] = s;
             }
         }
     }

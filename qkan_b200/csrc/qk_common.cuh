@@ -275,9 +275,10 @@ __device__ __forceinline__ float edge_forward(const EdgeFwd<R>& e, float x, floa
         vz = nz;
     }
     if (!FAST) return vz;
-    float s2 = fmaf(vx, vx, vy * vy);
+    // rho^2 with a 1e-30 floor folded into the sum (keeps 1/rho finite at the poles at no extra cost)
+    float s2 = fmaf(vx, vx, fmaf(vy, vy, 1e-30f));
     if (KEEP) {
-        inv_rho = qk_rsqrt<PRECISE>(fmaxf(s2, 1e-30f));
+        inv_rho = qk_rsqrt<PRECISE>(s2);
         r = qk_rsqrt<PRECISE>(fmaf(s2, inv_rho, 1.0f));
     } else {
         r = qk_rsqrt<PRECISE>(1.0f + qk_sqrt<PRECISE>(s2));
