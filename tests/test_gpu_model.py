@@ -187,3 +187,43 @@ def test_graphed_train_step_and_inference_match_eager():
         y2_e = model(x2)
     assert nerr(infer(x).cpu().numpy(), y_e.cpu().numpy()) <= 1e-6
     assert nerr(infer(x2).cpu().numpy(), y2_e.cpu().numpy()) <= 1e-6
+
+
+def test_loaded_mask_and_frozen_nonzero_bias_are_honoured():
+    """A checkpoint with a pruned mask and a non-zero (frozen) postact_bias must change the output accordingly."""
+    torch.manual_seed(1)
+    src = QKANLayer(6, 4, reps=2, seed=5, postact_bias_trainable=True, device="cuda")
+    with torch.no_grad():
+        src.postact_bias.normal_()
+        src.mask[1, 2] = 0.0
+        src.mask[3, 0] = 0.0
+    src._mask_is_identity = False
+    dst = QKANLayer(6, 4, reps=2, seed=9, postact_bias_trainable=False, device="cuda")  # bias frozen here
+    dst.load_state_dict(src.state_dict())
+    assert dst._pb_is_nonzero and not dst._mask_is_identity
+    x = torch.rand(10, 6, device="cuda") * 2 - 1
+    assert torch.allclose(src(x), dst(x), atol=1e-6)
+    ref = oracle.forward(x.cpu().numpy(), *(t.detach().double().cpu().numpy() for t in dst._expanded()),
+                         dst.postact_weights.detach().cpu().numpy(), dst.postact_bias.detach().cpu().numpy(),
+                         dst.base_weight.detach().cpu().numpy(), dst.mask.detach().cpu().numpy(),
+                         preact_trainable=False, use_postact_bias=True)
+    assert nerr(dst(x).detach().cpu().numpy(), ref) <= TOL_F32
+
+
+def test_train_loop_with_adam_pruning_and_grouped_theta():
+    """train_ with the default optimiser, theta-magnitude pruning, and grouped theta (pruning must skip it)."""
+    torch.manual_seed(0)
+    x = torch.rand(256, 3, device="cuda") * 2 - 1
+    y = (x[:, :1] * x[:, 1:2] + torch.sin(3 * x[:, 2:3])).contiguous()
+    dataset = dict(train_input=x, train_label=y, test_input=x[:128], test_label=y[:128])
+    model = QKAN([3, 5, 1], reps=2, seed=1, device="cuda")
+    with torch.no_grad():
+        model.layers[0].theta[0, 0].zero_()  # one edge below the pruning threshold
+    res = model.train_(dataset, steps=6, batch=128, verbose=False, prune_every=2, prune_threshold=1e-6,
+                       optimizer=torch.optim.Adam(model.parameters(), lr=1e-2))
+    assert len(res["train_loss"]) == 6 and np.isfinite(res["train_loss"]).all()
+    assert float(res["train_loss"][-1]) < float(res["train_loss"][0])
+    grouped = QKAN([3, 4, 1], reps=2, group=2, seed=1, device="cuda")
+    before = [layer.mask.clone() for layer in grouped.layers]
+    grouped.train_(dataset, steps=2, verbose=False, prune_every=1, prune_threshold=1e3)
+    assert all(torch.equal(a, layer.mask) for a, layer in zip(before, grouped.layers))

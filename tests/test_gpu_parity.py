@@ -169,3 +169,13 @@ def test_c_abi_rejects_bad_workspaces_and_null_pointers():
     assert lib.qk_pz_forward(_abi.desc_pointer(bad), *args, aligned, need, None) == _abi.QK_ERR_BAD_ARGUMENT
     assert lib.qk_pz_forward(dp, *args, aligned, need, None) == _abi.QK_OK
     torch.cuda.synchronize()
+
+
+@pytest.mark.parametrize("x_scale,precise", [(10.0, False), (10.0, True), (300.0, True)])
+def test_accuracy_for_large_input_magnitudes(x_scale, precise):
+    """|x| up to 10 stays inside 1e-5 on the special-function-unit path; the full-precision path also at |x| ~ 300."""
+    p = random_problem(77, 200, 48, 24, 3, use_pb=True, x_scale=x_scale)
+    cfg = dict(preact_trainable=True, fast_measure=True, use_postact_bias=True)
+    y, g = _run_cuda(p, cfg, precise=precise)
+    y_ref, g_ref = _run_oracle(p, cfg)
+    _check(y, g, y_ref, g_ref, TOL_F32, f"x_scale {x_scale} precise {precise}")
