@@ -138,6 +138,68 @@ class QKAN(nn.Module):
             x = F.normalize(x, p=self.norm_out, dim=1)
         return x.reshape(*lead, x.shape[1])
 
+    # ------------------------------------------------------------------ layer extension
+    def initialize_parameters(self) -> "QKAN":
+        """Reset every QKAN layer in place (theta to zero, the rest to defaults)."""
+        for layer in self.layers:
+            if isinstance(layer, QKANLayer):
+                layer.reset_parameters()
+        return self
+
+    def xavier_init(self) -> "QKAN":
+        for layer in self.layers:
+            if isinstance(layer, QKANLayer):
+                layer.xavier_init()
+        return self
+
+    def initialize_from_another_model(self, another_model: "QKAN") -> "QKAN":
+        """Copy a model with fewer repetitions into this one (``src/qkan/qkan.py:1315-1366``).
+
+        The source's circuit layers fill the leading layers here and the added layers stay at zero
+        angles. For pz / rpz the added gates are then Rz rotations in front of a Z readout and zero
+        Ry rotations, which leave the readout unchanged: the extended model starts as the same function.
+        """
+        assert list(self.width) == list(another_model.width), \
+            "Cannot initialize from another model with different width"
+        linear_src = [m for m in another_model.layers if isinstance(m, nn.Linear)]
+        linear_dst = [m for m in self.layers if isinstance(m, nn.Linear)]
+        with torch.no_grad():
+            for dst, src in zip(self.layers, another_model.layers):
+                if not isinstance(dst, QKANLayer):
+                    continue
+                assert isinstance(src, QKANLayer)
+                dst.reset_parameters()
+                n_theta = src._theta_natural().shape[-2]
+                dst._theta_natural()[..., :n_theta, :].copy_(src._theta_natural())
+                dst._preacts_w_natural()[..., : src.reps].copy_(src._preacts_w_natural())
+                dst._preacts_b_natural()[..., : src.reps].copy_(src._preacts_b_natural())
+                for name in ("postact_weights", "postact_bias", "base_weight"):
+                    dst._as_oi(getattr(dst, name)).copy_(src._as_oi(getattr(src, name)))
+                dst._pb_is_nonzero = bool(dst.postact_bias.any())
+                dst._bw_is_nonzero = bool(dst.ba_trainable or dst.base_weight.any())
+            for dst, src in zip(linear_dst, linear_src):
+                dst.weight.copy_(src.weight)
+                dst.bias.copy_(src.bias)
+        return self
+
+    def refine(self, new_reps: int) -> "QKAN":
+        """New model with ``new_reps > reps`` repetitions that starts as the same function (layer extension)."""
+        assert new_reps > self.reps, "New repetitions must be greater than current repetitions"
+        new_model = QKAN(
+            width=self.width, reps=new_reps, group=self.group, device=self.device, solver=self.solver,
+            qml_device=self.qml_device, ansatz=self.ansatz, theta_size=self.theta_size, norm_out=self.norm_out,
+            preact_trainable=self.preact_trainable, preact_init=self.preact_init,
+            postact_weight_trainable=self.postact_weight_trainable,
+            postact_bias_trainable=self.postact_bias_trainable, base_activation=self.base_activation,
+            ba_trainable=self.ba_trainable, is_batchnorm=self.is_batchnorm, is_map=self.is_map,
+            hidden=self.hidden, fast_measure=self.fast_measure, save_act=self.save_act, c_dtype=self.c_dtype,
+            p_dtype=self.p_dtype, seed=self.seed, solver_kwargs=self.solver_kwargs, p_dim=self.p_dim,
+            theta_init=self.theta_init)
+        return new_model.initialize_from_another_model(self)
+
+    def layer_extension(self, new_reps: int) -> "QKAN":
+        return self.refine(new_reps)
+
     # ------------------------------------------------------------------ regulariser used by train_
     def get_reg(self, reg_metric: str, lamb_l1: float, lamb_entropy: float, lamb_coef: float,
                 lamb_coefdiff: float) -> torch.Tensor:

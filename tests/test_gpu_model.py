@@ -227,3 +227,19 @@ def test_train_loop_with_adam_pruning_and_grouped_theta():
     before = [layer.mask.clone() for layer in grouped.layers]
     grouped.train_(dataset, steps=2, verbose=False, prune_every=1, prune_threshold=1e3)
     assert all(torch.equal(a, layer.mask) for a, layer in zip(before, grouped.layers))
+
+
+@pytest.mark.parametrize("ansatz", ["pz_encoding", "rpz_encoding"])
+def test_refine_is_function_preserving(ansatz):
+    """Layer extension: the model with more repetitions starts as exactly the same function."""
+    torch.manual_seed(0)
+    model = QKAN([5, 6, 2], reps=2, seed=4, ansatz=ansatz, preact_trainable=True, ba_trainable=True,
+                 postact_bias_trainable=True, device="cuda")
+    with torch.no_grad():
+        for p in model.parameters():
+            if p.requires_grad:
+                p.add_(0.1 * torch.randn_like(p))
+    x = torch.rand(32, 5, device="cuda") * 2 - 1
+    bigger = model.refine(5)
+    assert bigger.layers[0].reps == 5 and bigger.layers[0].theta.shape[2] == 6
+    assert nerr(bigger(x).detach().cpu().numpy(), model(x).detach().cpu().numpy()) <= 1e-6

@@ -117,3 +117,29 @@ def test_parameter_shapes_of_the_other_ansaetze_follow_the_reference():
     real = QKANLayer(4, 3, reps=2, ansatz="real", p_dim=2)
     assert real.theta.shape == (12, 2) and real._theta_natural().shape == (3, 4, 2, 1)
     assert real.c_dtype == torch.bfloat16
+
+
+def test_refine_copies_the_leading_circuit_layers_and_zeroes_the_rest():
+    """Layer extension (reference: src/qkan/qkan.py:1315-1445): old layers first, added layers at zero angles."""
+    small = QKAN([3, 4, 2], reps=2, seed=1, preact_trainable=True, is_map=True, hidden=3)
+    with torch.no_grad():
+        for p in small.parameters():
+            p.add_(0.25)
+    big = small.layer_extension(4)
+    assert big.reps == 4 and list(big.width) == list(small.width)
+    for dst, src in zip(big.layers, small.layers):
+        if isinstance(dst, QKANLayer):
+            assert dst.reps == 4 and tuple(dst.theta.shape) == (dst.out_dim, dst.in_dim, 5, 2)
+            assert torch.equal(dst.theta[:, :, :3], src.theta)
+            assert not dst.theta[:, :, 3:].any()
+            assert torch.equal(dst.preacts_weight[..., :2], src.preacts_weight)
+            assert torch.equal(dst.preacts_bias[..., :2], src.preacts_bias)
+            for name in ("postact_weights", "postact_bias", "base_weight"):
+                assert torch.equal(getattr(dst, name), getattr(src, name))
+        elif isinstance(dst, torch.nn.Linear):
+            assert torch.equal(dst.weight, src.weight) and torch.equal(dst.bias, src.bias)
+    with pytest.raises(AssertionError):
+        small.refine(2)
+    with pytest.raises(AssertionError):
+        QKAN([3, 5, 2], reps=4).initialize_from_another_model(small)
+    assert not big.initialize_parameters().layers[0].theta.any()
