@@ -24,7 +24,7 @@
 extern "C" {
 #endif
 
-#define QK_ABI_VERSION 2
+#define QK_ABI_VERSION 3
 
 enum QkDtype { QK_F32 = 0, QK_BF16 = 1 };
 
@@ -63,6 +63,11 @@ typedef struct QkDesc {
     int32_t param_dtype; /* QkDtype of postact_weights, postact_bias, base_weight, mask */
     uint32_t flags;      /* QkFlags */
     int32_t ansatz;      /* QkAnsatz */
+    int32_t group;       /* 0: theta / preacts hold one entry per edge, shapes (O,I,...).
+                            g > 0: grouped parameters (QKANLayer `group=g`, src/qkan/qkan.py:246-308):
+                            theta is (g,...) and preacts are (g,R); edge (o,i) uses entry i mod g for every o
+                            (the broadcast of src/qkan/solver/exact.py:68-86), and grad_theta / grad_preacts_*
+                            come back in the grouped shapes, summed over the edges that share an entry. */
 } QkDesc;
 
 /* ABI version of the loaded library (compare with QK_ABI_VERSION). */

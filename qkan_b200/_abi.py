@@ -9,7 +9,7 @@ import ctypes
 import os
 from ctypes import Structure, c_char_p, c_int, c_int32, c_size_t, c_uint32, c_void_p
 
-QK_ABI_VERSION = 2
+QK_ABI_VERSION = 3
 
 QK_F32 = 0
 QK_BF16 = 1
@@ -60,6 +60,7 @@ class QkDesc(Structure):
         ("param_dtype", c_int32),
         ("flags", c_uint32),
         ("ansatz", c_int32),
+        ("group", c_int32),
     ]
 
 

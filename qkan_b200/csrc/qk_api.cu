@@ -37,6 +37,8 @@ int check_desc(const QkDesc* d) {
                     d->param_dtype);
     if (d->flags & ~(QK_PREACT_TRAINABLE | QK_FAST_MEASURE | QK_USE_POSTACT_BIAS | QK_PRECISE_MATH))
         return fail(QK_ERR_BAD_ARGUMENT, "unknown flag bits 0x%x", d->flags);
+    if (d->group < 0) return fail(QK_ERR_BAD_ARGUMENT, "group must be >= 0 (got %d)", d->group);
+    if (d->group > 65535) return fail(QK_ERR_UNSUPPORTED, "group %d exceeds 65535", d->group);
     if ((long long)d->out_dim > 65535)
         return fail(QK_ERR_UNSUPPORTED, "out_dim %d exceeds 65535", d->out_dim);
     return QK_OK;
@@ -55,8 +57,14 @@ bool use_xtrig(const QkDesc& d) {
 struct Layout {
     int ipad;
     size_t table_off, bias_off, colsum_off, partials_off, total;
+    size_t gtheta_off, gpw_off, gpb_off;  // per-edge gradients ahead of the group reduction (group > 0)
     int ncolsplit;
 };
+
+size_t theta_per_entry(const QkDesc& d) {
+    return d.ansatz == QK_ANSATZ_PZ ? (size_t)(d.reps + 1) * 2
+                                    : (d.ansatz == QK_ANSATZ_RPZ ? (size_t)d.reps + 1 : (size_t)d.reps);
+}
 
 Layout forward_layout(const QkDesc& d) {
     Layout l{};
@@ -77,6 +85,13 @@ Layout backward_layout(const QkDesc& d, bool base) {
     l.partials_off = l.colsum_off + qk::align256((size_t)l.ncolsplit * d.out_dim * sizeof(float));
     l.total = l.partials_off +
               qk::align256((size_t)c.grid_b * d.out_dim * c.nacc * l.ipad * sizeof(float));
+    if (d.group > 0) {
+        const size_t nE = (size_t)d.out_dim * d.in_dim;
+        l.gtheta_off = l.total;
+        l.gpw_off = l.gtheta_off + qk::align256(nE * theta_per_entry(d) * sizeof(float));
+        l.gpb_off = l.gpw_off + qk::align256(nE * d.reps * sizeof(float));
+        l.total = l.gpb_off + qk::align256(nE * d.reps * sizeof(float));
+    }
     return l;
 }
 
@@ -131,6 +146,7 @@ int run_forward(const QkDesc* desc, const void* x, const float* theta, const flo
     p.mask = edges ? nullptr : mask;
     p.table = reinterpret_cast<float*>(wsb + l.table_off);
     p.bias = edges ? nullptr : reinterpret_cast<float*>(wsb + l.bias_off);
+    p.group = d.group;
     const bool xtrig = use_xtrig(d);
     p.xtrig = xtrig;
     cudaError_t e = qk::launch_prep(p, st);
@@ -172,11 +188,10 @@ int run_backward(const QkDesc* desc, const void* x, const float* theta, const fl
         cudaError_t e = cudaSuccess;
         size_t es = d.io_dtype == QK_BF16 ? 2 : 4;
         if (gx && (size_t)d.batch * d.in_dim) e = cudaMemsetAsync(gx, 0, (size_t)d.batch * d.in_dim * es, st);
-        const size_t theta_per_edge = d.ansatz == QK_ANSATZ_PZ ? (size_t)(d.reps + 1) * 2
-                                      : (d.ansatz == QK_ANSATZ_RPZ ? (size_t)d.reps + 1 : (size_t)d.reps);
-        if (e == cudaSuccess && gtheta && nE) e = cudaMemsetAsync(gtheta, 0, nE * theta_per_edge * 4, st);
-        if (e == cudaSuccess && gpw && nE) e = cudaMemsetAsync(gpw, 0, nE * d.reps * 4, st);
-        if (e == cudaSuccess && gpb && nE) e = cudaMemsetAsync(gpb, 0, nE * d.reps * 4, st);
+        const size_t nQ = d.group > 0 ? (size_t)d.group : nE;  // entries of theta / preacts
+        if (e == cudaSuccess && gtheta && nQ) e = cudaMemsetAsync(gtheta, 0, nQ * theta_per_entry(d) * 4, st);
+        if (e == cudaSuccess && gpw && nQ) e = cudaMemsetAsync(gpw, 0, nQ * d.reps * 4, st);
+        if (e == cudaSuccess && gpb && nQ) e = cudaMemsetAsync(gpb, 0, nQ * d.reps * 4, st);
         if (e == cudaSuccess && gpostw && nE) e = cudaMemsetAsync(gpostw, 0, nE * 4, st);
         if (e == cudaSuccess && gpostb && nE) e = cudaMemsetAsync(gpostb, 0, nE * 4, st);
         if (e == cudaSuccess && gbasew && nE) e = cudaMemsetAsync(gbasew, 0, nE * 4, st);
@@ -212,6 +227,7 @@ int run_backward(const QkDesc* desc, const void* x, const float* theta, const fl
     p.table = reinterpret_cast<float*>(wsb + l.table_off);
     p.bias = nullptr;
     p.xtrig = 0;
+    p.group = d.group;
     cudaError_t e = qk::launch_prep(p, st);
     if (e != cudaSuccess) return cuda_fail(e, "prep launch");
 
@@ -262,14 +278,25 @@ int run_backward(const QkDesc* desc, const void* x, const float* theta, const fl
         f.postw = edges ? nullptr : postw;
         f.postb = edges ? nullptr : postb;
         f.mask = edges ? nullptr : mask;
-        f.gtheta = gtheta;
-        f.gpw = gpw;
-        f.gpb = gpb;
+        // grouped parameters: per-edge gradients go to scratch and are summed per entry afterwards
+        const bool grouped = d.group > 0;
+        f.gtheta = grouped && gtheta ? reinterpret_cast<float*>(wsb + l.gtheta_off) : gtheta;
+        f.gpw = grouped && gpw ? reinterpret_cast<float*>(wsb + l.gpw_off) : gpw;
+        f.gpb = grouped && gpb ? reinterpret_cast<float*>(wsb + l.gpb_off) : gpb;
         f.gpostw = edges ? nullptr : gpostw;
         f.gpostb = edges ? nullptr : gpostb;
         f.gbasew = edges ? nullptr : gbasew;
         e = qk::launch_finish(f, st);
         if (e != cudaSuccess) return cuda_fail(e, "finish launch");
+        if (grouped) {
+            const int per_theta = (int)theta_per_entry(d);
+            if (gtheta) e = qk::launch_group_reduce(f.gtheta, gtheta, d.out_dim, d.in_dim, d.group, per_theta, st);
+            if (e == cudaSuccess && gpw)
+                e = qk::launch_group_reduce(f.gpw, gpw, d.out_dim, d.in_dim, d.group, d.reps, st);
+            if (e == cudaSuccess && gpb)
+                e = qk::launch_group_reduce(f.gpb, gpb, d.out_dim, d.in_dim, d.group, d.reps, st);
+            if (e != cudaSuccess) return cuda_fail(e, "group reduction launch");
+        }
     }
     return QK_OK;
 }

@@ -10,6 +10,7 @@ struct PrepArgs {
     int rk;      // compiled_reps(ansatz, reps): the table is laid out for this repetition count
     int ansatz;  // QkAnsatz
     int xtrig;   // frozen-preact forward: rows (pw_l, c_l) hold (cos c_l, sin c_l) instead
+    int group;   // > 0: theta / preacts are grouped, edge (o,i) reads entry i % group
     unsigned flags;
     int param_dtype;
     const float* theta;
@@ -90,6 +91,9 @@ cudaError_t launch_prep(const PrepArgs& a, cudaStream_t st);
 cudaError_t launch_colsum(const void* gy, int io_dtype, int B, int O, int nsplit, float* part,
                           cudaStream_t st);
 cudaError_t launch_finish(const FinishArgs& a, cudaStream_t st);
+// dst[k*per + c] = sum over o and over i == k (mod group) of src[(o*in_dim + i)*per + c], fixed order
+cudaError_t launch_group_reduce(const float* src, float* dst, int out_dim, int in_dim, int group, int per,
+                                cudaStream_t st);
 cudaError_t launch_forward(const FwdArgs& a, int reps, bool fast, int io_dtype, bool has_base,
                            cudaStream_t st);
 cudaError_t launch_backward(const BwdArgs& a, int reps, bool fast, int io_dtype, bool has_base,

@@ -21,6 +21,7 @@ __global__ void prep_table_kernel(PrepArgs a) {
         return;
     }
     const size_t e = (size_t)o * a.in_dim + i;
+    const size_t q = a.group > 0 ? (size_t)(i % a.group) : e;  // entry of theta / preacts this edge reads
     const float m = a.mask ? ld_param(a.mask, a.param_dtype, e) : 1.f;
     const float w = a.postw ? ld_param(a.postw, a.param_dtype, e) * m : 1.f;
     const float bw = a.basew ? ld_param(a.basew, a.param_dtype, e) * m : 0.f;
@@ -29,11 +30,11 @@ __global__ void prep_table_kernel(PrepArgs a) {
 
     if (a.ansatz == QK_ANSATZ_REAL) {
         // alpha = A x + C; C is reduced to [-pi, pi] in double so the SFU sees a small argument
-        const float* th = a.theta + e * R;
+        const float* th = a.theta + q * R;
         double A = 0.0, C = 1.5707963267948966;
         for (int l = 0; l < R; ++l) {
-            A += ptr ? (double)a.pw[e * R + l] : 1.0;
-            C += (ptr ? (double)a.pb[e * R + l] : 0.0) - (double)th[l] - 3.141592653589793;
+            A += ptr ? (double)a.pw[q * R + l] : 1.0;
+            C += (ptr ? (double)a.pb[q * R + l] : 0.0) - (double)th[l] - 3.141592653589793;
         }
         C -= 6.283185307179586 * rint(C / 6.283185307179586);
         for (int k = 0; k < K; ++k) put(k, 0.f);
@@ -46,7 +47,7 @@ __global__ void prep_table_kernel(PrepArgs a) {
 
     const bool pz = a.ansatz == QK_ANSATZ_PZ;
     const int ts = pz ? 2 : 1;  // floats of theta per layer
-    const float* th = a.theta + e * (R + 1) * ts;
+    const float* th = a.theta + q * (R + 1) * ts;
     auto th_ry = [&](int l) { return pz ? th[2 * l + 1] : th[l]; };   // Ry angle of layer l
     auto th_rz = [&](int l) { return pz ? th[2 * l] : 0.f; };          // Rz angle of layer l (pz only)
     float s00, c00, sa0, ca0;
@@ -65,8 +66,8 @@ __global__ void prep_table_kernel(PrepArgs a) {
             put(t_pw(l), c);
             put(t_c(l), s);
         } else if (l < R) {
-            put(t_pw(l), ptr ? a.pw[e * R + l] : 1.f);
-            put(t_c(l), (ptr ? a.pb[e * R + l] : 0.f) + th_rz(l + 1));
+            put(t_pw(l), ptr ? a.pw[q * R + l] : 1.f);
+            put(t_c(l), (ptr ? a.pb[q * R + l] : 0.f) + th_rz(l + 1));
         } else {  // identity padding
             put(t_pw(l), 0.f);
             put(t_c(l), 0.f);
@@ -192,6 +193,35 @@ __global__ void finish_grads_kernel(FinishArgs a) {
         }
         if (a.gbasew) a.gbasew[e] = a.has_base ? m * total(a_bw(RK)) : 0.f;
     }
+}
+
+// One CTA per (group entry k, component c): threads take the (o, j) pairs, i = k + j*group, in a fixed
+// strided order and a shared-memory tree adds them, so the result is run-to-run reproducible.
+__global__ void group_reduce_kernel(const float* __restrict__ src, float* __restrict__ dst, int out_dim,
+                                    int in_dim, int group, int per) {
+    __shared__ float sm[256];
+    const int k = blockIdx.x, c = blockIdx.y;
+    const int nj = (in_dim - k + group - 1) / group;  // inputs i = k, k+group, ... < in_dim
+    const long long n = (long long)out_dim * nj;
+    float s = 0.f;
+    for (long long idx = threadIdx.x; idx < n; idx += blockDim.x) {
+        const int o = (int)(idx / nj), j = (int)(idx - (long long)o * nj);
+        s += src[((size_t)o * in_dim + k + (size_t)j * group) * per + c];
+    }
+    sm[threadIdx.x] = s;
+    __syncthreads();
+    for (int d = 128; d >= 1; d >>= 1) {
+        if (threadIdx.x < d) sm[threadIdx.x] += sm[threadIdx.x + d];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) dst[(size_t)k * per + c] = sm[0];
+}
+
+cudaError_t launch_group_reduce(const float* src, float* dst, int out_dim, int in_dim, int group, int per,
+                                cudaStream_t st) {
+    dim3 grid(group, per);
+    group_reduce_kernel<<<grid, 256, 0, st>>>(src, dst, out_dim, in_dim, group, per);
+    return cudaPeekAtLastError();
 }
 
 cudaError_t launch_prep(const PrepArgs& a, cudaStream_t st) {

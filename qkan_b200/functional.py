@@ -85,17 +85,36 @@ def _ansatz_code(ansatz) -> int:
             f"ansatz {ansatz!r}: the B200 kernels implement pz_encoding, rpz_encoding and real") from None
 
 
-def _make_desc(x, theta, flags, param_dtype, ansatz="pz_encoding") -> _abi.QkDesc:
-    """Descriptor from the tensor shapes; theta is (O,I,R+1,2) pz, (O,I,R+1,1) rpz, (O,I,R,1) real."""
+def _make_desc(x, theta, flags, param_dtype, ansatz="pz_encoding", out_dim: Optional[int] = None) -> _abi.QkDesc:
+    """Descriptor from the tensor shapes.
+
+    Per-edge theta is (O,I,R+1,2) pz, (O,I,R+1,1) rpz, (O,I,R,1) real. Grouped theta drops the (O,I) axes
+    for one group axis, ``(g, ...)``: edge (o,i) uses entry ``i mod g`` (``src/qkan/solver/exact.py:68-86``);
+    the number of outputs then comes from ``out_dim``.
+    """
     code = _ansatz_code(ansatz)
     B, I = x.shape
-    if theta.dim() != 4:
-        raise ValueError(f"theta must have 4 dimensions, got {tuple(theta.shape)}")
-    O, I2, layers, width = theta.shape
-    if I2 != I or width != (2 if code == _abi.QK_ANSATZ_PZ else 1):
-        raise ValueError(f"theta {tuple(theta.shape)} does not match x {tuple(x.shape)} for ansatz {ansatz!r}")
+    width_want = 2 if code == _abi.QK_ANSATZ_PZ else 1
+    if theta.dim() == 3:
+        group, layers, width = theta.shape
+        if out_dim is None or group < 1:
+            raise ValueError("grouped theta (3 dimensions) needs out_dim and at least one group entry")
+        O = int(out_dim)
+    elif theta.dim() == 4:
+        O, I2, layers, width = theta.shape
+        group = 0
+        if I2 != I or (out_dim is not None and out_dim != O):
+            raise ValueError(f"theta {tuple(theta.shape)} does not match x {tuple(x.shape)} / out_dim {out_dim}")
+    else:
+        raise ValueError(f"theta must have 4 dimensions (3 when grouped), got {tuple(theta.shape)}")
+    if width != width_want:
+        raise ValueError(f"theta {tuple(theta.shape)} does not match ansatz {ansatz!r}")
     reps = layers if code == _abi.QK_ANSATZ_REAL else layers - 1
-    return _abi.QkDesc(B, I, O, reps, _io_dtype(x), param_dtype, flags, code)
+    return _abi.QkDesc(B, I, O, reps, _io_dtype(x), param_dtype, flags, code, group)
+
+
+def _preact_shape(desc: _abi.QkDesc):
+    return (desc.group, desc.reps) if desc.group else (desc.out_dim, desc.in_dim, desc.reps)
 
 
 def layer_forward(x, theta, pw, pb, postw, postb=None, basew=None, mask=None, *,
@@ -108,8 +127,9 @@ def layer_forward(x, theta, pw, pb, postw, postb=None, basew=None, mask=None, *,
     x = x.detach().contiguous()
     theta, pw, pb = _f32c(theta), _f32c(pw), _f32c(pb)
     postw, postb, basew, mask, pdt = _oi_params(postw, postb if use_postact_bias else None, basew, mask)
-    desc = _make_desc(x, theta, _flags(preact_trainable, fast_measure, use_postact_bias and postb is not None, precise), pdt, ansatz)
-    y = torch.empty((x.shape[0], theta.shape[0]), dtype=x.dtype, device=x.device)
+    desc = _make_desc(x, theta, _flags(preact_trainable, fast_measure, use_postact_bias and postb is not None, precise), pdt, ansatz,
+                      out_dim=postw.shape[0])
+    y = torch.empty((x.shape[0], desc.out_dim), dtype=x.dtype, device=x.device)
     with torch.cuda.device(x.device):
         nbytes = lib.qk_forward_workspace_bytes(_abi.desc_pointer(desc))
         ws = _workspace(x.device, nbytes)
@@ -136,11 +156,12 @@ def layer_backward(x, theta, pw, pb, postw, postb, basew, mask, gy, *, preact_tr
     gy = gy.detach().to(x.dtype).contiguous()
     theta, pw, pb = _f32c(theta), _f32c(pw), _f32c(pb)
     postw, postb, basew, mask, pdt = _oi_params(postw, postb if use_postact_bias else None, basew, mask)
-    desc = _make_desc(x, theta, _flags(preact_trainable, fast_measure, use_postact_bias and postb is not None, precise), pdt, ansatz)
-    O, I = theta.shape[:2]
+    desc = _make_desc(x, theta, _flags(preact_trainable, fast_measure, use_postact_bias and postb is not None, precise), pdt, ansatz,
+                      out_dim=postw.shape[0])
+    O, I = desc.out_dim, desc.in_dim
     dev = x.device
-    shapes = {"x": tuple(x.shape), "theta": tuple(theta.shape), "preacts_weight": (O, I, desc.reps),
-              "preacts_bias": (O, I, desc.reps), "postact_weights": (O, I), "postact_bias": (O, I),
+    shapes = {"x": tuple(x.shape), "theta": tuple(theta.shape), "preacts_weight": _preact_shape(desc),
+              "preacts_bias": _preact_shape(desc), "postact_weights": (O, I), "postact_bias": (O, I),
               "base_weight": (O, I)}
     given = out or {}
     out = {}
@@ -168,14 +189,15 @@ def layer_backward(x, theta, pw, pb, postw, postb, basew, mask, gy, *, preact_tr
 
 
 def postacts_forward(x, theta, pw, pb, *, preact_trainable: bool, fast_measure: bool = True,
-                     ansatz: str = "pz_encoding", precise: bool = False) -> torch.Tensor:
-    """Per-edge activations ``(B,O,I)`` (solver contract); no autograd."""
+                     ansatz: str = "pz_encoding", precise: bool = False,
+                     out_dim: Optional[int] = None) -> torch.Tensor:
+    """Per-edge activations ``(B,O,I)`` (solver contract); no autograd. ``out_dim`` is needed for grouped theta."""
     lib = _abi.load()
     _require_cuda(x, "x")
     x = x.detach().contiguous()
     theta, pw, pb = _f32c(theta), _f32c(pw), _f32c(pb)
-    desc = _make_desc(x, theta, _flags(preact_trainable, fast_measure, False, precise), _abi.QK_F32, ansatz)
-    out = torch.empty((x.shape[0], theta.shape[0], x.shape[1]), dtype=x.dtype, device=x.device)
+    desc = _make_desc(x, theta, _flags(preact_trainable, fast_measure, False, precise), _abi.QK_F32, ansatz, out_dim)
+    out = torch.empty((x.shape[0], desc.out_dim, x.shape[1]), dtype=x.dtype, device=x.device)
     with torch.cuda.device(x.device):
         nbytes = lib.qk_forward_workspace_bytes(_abi.desc_pointer(desc))
         ws = _workspace(x.device, nbytes)
@@ -189,14 +211,14 @@ def postacts_forward(x, theta, pw, pb, *, preact_trainable: bool, fast_measure: 
 def postacts_backward(x, theta, pw, pb, gpostacts, *, preact_trainable: bool,
                       fast_measure: bool = True,
                       want=("x", "theta", "preacts_weight", "preacts_bias"),
-                      ansatz: str = "pz_encoding", precise: bool = False) -> dict:
+                      ansatz: str = "pz_encoding", precise: bool = False,
+                      out_dim: Optional[int] = None) -> dict:
     lib = _abi.load()
     _require_cuda(x, "x")
     x = x.detach().contiguous()
     gpostacts = gpostacts.detach().to(x.dtype).contiguous()
     theta, pw, pb = _f32c(theta), _f32c(pw), _f32c(pb)
-    desc = _make_desc(x, theta, _flags(preact_trainable, fast_measure, False, precise), _abi.QK_F32, ansatz)
-    O, I = theta.shape[:2]
+    desc = _make_desc(x, theta, _flags(preact_trainable, fast_measure, False, precise), _abi.QK_F32, ansatz, out_dim)
     f32 = dict(dtype=torch.float32, device=x.device)
     out = {}
     if "x" in want:
@@ -204,9 +226,9 @@ def postacts_backward(x, theta, pw, pb, gpostacts, *, preact_trainable: bool,
     if "theta" in want:
         out["theta"] = torch.empty(tuple(theta.shape), **f32)
     if "preacts_weight" in want:
-        out["preacts_weight"] = torch.empty((O, I, desc.reps), **f32)
+        out["preacts_weight"] = torch.empty(_preact_shape(desc), **f32)
     if "preacts_bias" in want:
-        out["preacts_bias"] = torch.empty((O, I, desc.reps), **f32)
+        out["preacts_bias"] = torch.empty(_preact_shape(desc), **f32)
     with torch.cuda.device(x.device):
         nbytes = lib.qk_backward_workspace_bytes(_abi.desc_pointer(desc))
         ws = _workspace(x.device, nbytes)
@@ -271,28 +293,29 @@ def qkan_layer(x, theta, preacts_weight, preacts_bias, postact_weights, postact_
     """
     return _LayerFunction.apply(x, theta, preacts_weight, preacts_bias, postact_weights,
                                 postact_bias, base_weight, mask, preact_trainable, fast_measure,
-                                use_postact_bias, ansatz, resolve_precise(precise, x, theta.shape[0]))
+                                use_postact_bias, ansatz, resolve_precise(precise, x, postact_weights.shape[0]))
 
 
 class _PostactsFunction(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, theta, pw, pb, preact_trainable, fast_measure, ansatz, precise):
+    def forward(ctx, x, theta, pw, pb, preact_trainable, fast_measure, ansatz, precise, out_dim):
         ctx.save_for_backward(x, theta, pw, pb)
-        ctx.cfg = (preact_trainable, fast_measure, ansatz, precise)
+        ctx.cfg = (preact_trainable, fast_measure, ansatz, precise, out_dim)
         return postacts_forward(x, theta, pw, pb, preact_trainable=preact_trainable,
-                                fast_measure=fast_measure, ansatz=ansatz, precise=precise)
+                                fast_measure=fast_measure, ansatz=ansatz, precise=precise, out_dim=out_dim)
 
     @staticmethod
     def backward(ctx, gpa):
         x, theta, pw, pb = ctx.saved_tensors
-        preact_trainable, fast_measure, ansatz, precise = ctx.cfg
+        preact_trainable, fast_measure, ansatz, precise, out_dim = ctx.cfg
         names = ("x", "theta", "preacts_weight", "preacts_bias")
         need = ctx.needs_input_grad
         want = tuple(n for k, n in enumerate(names) if need[k])
         if not _uses_preacts(preact_trainable, ansatz):
             want = tuple(n for n in want if n not in ("preacts_weight", "preacts_bias"))
         g = postacts_backward(x, theta, pw, pb, gpa, preact_trainable=preact_trainable,
-                              fast_measure=fast_measure, want=want, ansatz=ansatz, precise=precise)
+                              fast_measure=fast_measure, want=want, ansatz=ansatz, precise=precise,
+                              out_dim=out_dim)
         srcs = (x, theta, pw, pb)
         outs = []
         for k, n in enumerate(names):
@@ -300,11 +323,15 @@ class _PostactsFunction(torch.autograd.Function):
             if t is not None:
                 t = t.to(srcs[k].dtype).reshape(srcs[k].shape)
             outs.append(t)
-        return (*outs, None, None, None, None)
+        return (*outs, None, None, None, None, None)
 
 
 def qkan_postacts(x, theta, preacts_weight, preacts_bias, *, preact_trainable: bool,
-                  fast_measure: bool = True, ansatz: str = "pz_encoding", precise="auto") -> torch.Tensor:
-    """Differentiable per-edge activations ``(B,O,I)`` — the reference solver contract."""
+                  fast_measure: bool = True, ansatz: str = "pz_encoding", precise="auto",
+                  out_dim: Optional[int] = None) -> torch.Tensor:
+    """Differentiable per-edge activations ``(B,O,I)`` — the reference solver contract.
+
+    Grouped theta / preacts ``(g, ...)`` are read in place (pass ``out_dim``); their gradients come back grouped."""
+    O = theta.shape[0] if theta.dim() == 4 else out_dim
     return _PostactsFunction.apply(x, theta, preacts_weight, preacts_bias, preact_trainable,
-                                   fast_measure, ansatz, resolve_precise(precise, x, theta.shape[0]))
+                                   fast_measure, ansatz, resolve_precise(precise, x, O), out_dim)

@@ -234,11 +234,20 @@ class QKANLayer(nn.Module):
         """Kept for interface compatibility: the epilogue is always fused into the kernel here."""
 
     # ------------------------------------------------------------------ forward
-    def _expanded(self):
-        """theta / preacts in the (O, I, ...) rank the kernels read.
+    def _kernel_params(self):
+        """theta / preacts as the kernels take them: per edge ``(O, I, ...)``, or grouped ``(g, ...)``.
 
-        Grouped parameters are broadcast with ``repeat`` exactly as the reference solvers do
-        (``src/qkan/solver/exact.py:68-86``) so that autograd sums the gradients over the group.
+        A single group axis is passed through as it is: the kernels read entry ``i mod g`` for edge (o, i)
+        (the broadcast of ``src/qkan/solver/exact.py:68-86``) and return the gradients already summed per entry.
+        """
+        theta, pw, pb = self._theta_natural(), self._preacts_w_natural(), self._preacts_b_natural()
+        if theta.dim() == 3 and pw.dim() == 2:
+            return theta, pw, pb
+        return self._expanded()
+
+    def _expanded(self):
+        """theta / preacts materialised in the per-edge rank ``(O, I, ...)`` with ``repeat``, exactly as the
+        reference solvers do (``src/qkan/solver/exact.py:68-86``); autograd then sums the gradients over the group.
         """
         theta, pw, pb = self._theta_natural(), self._preacts_w_natural(), self._preacts_b_natural()
         if theta.dim() != 4:
@@ -262,7 +271,7 @@ class QKANLayer(nn.Module):
         self._check_solver()
         if self.is_batchnorm:
             x = self.bn(x)
-        theta, pw, pb = self._expanded()
+        theta, pw, pb = self._kernel_params()
         use_pb = self.postact_bias_trainable or self._pb_is_nonzero
         mask = None if self._mask_is_identity else self._as_oi(self.mask)
         base_w = self._as_oi(self.base_weight)
@@ -285,9 +294,9 @@ class QKANLayer(nn.Module):
         """Per-edge outputs ``(B, O, I)`` before the sum over inputs (``src/qkan/qkan.py:835-891``)."""
         assert x.shape[1] == self.in_dim, "Invalid input dimension"
         self._check_solver()
-        theta, pw, pb = self._expanded()
+        theta, pw, pb = self._kernel_params()
         postacts = qf.postacts_forward(x, theta, pw, pb, preact_trainable=self.preact_trainable,
-                                       fast_measure=self.fast_measure, ansatz=self.ansatz,
+                                       fast_measure=self.fast_measure, ansatz=self.ansatz, out_dim=self.out_dim,
                                        precise=qf.resolve_precise(self.solver_kwargs.get("precise", "auto"), x,
                                                                   self.out_dim)).to(self.p_dtype)
         base = torch.einsum("oi,bi->boi", self._as_oi(self.base_weight), self.base_activation(x))

@@ -30,7 +30,16 @@ class B200Solver:
         fast = kwargs.get("fast_measure", True)
         batch, in_dim = x.shape
         out_dim = kwargs.get("out_dim", in_dim)
-        # group broadcasting as the reference solvers do it (src/qkan/solver/exact.py:68-86)
+        layers = reps if ansatz == "real" else reps + 1
+        if theta.dim() == 3 and preacts_weight.dim() == 2 and theta.shape[0] == preacts_weight.shape[0]:
+            # grouped parameters (g, ...): the kernels index entry i mod g themselves and reduce the
+            # gradients per entry, so nothing of size (O, I, ...) is materialised
+            if theta.shape[1] != layers:
+                raise ValueError(f"theta holds {theta.shape[1]} layers, reps={reps} needs {layers}")
+            return qf.qkan_postacts(x, theta, preacts_weight, preacts_bias, preact_trainable=trainable,
+                                    fast_measure=fast, ansatz=ansatz, precise=kwargs.get("precise", "auto"),
+                                    out_dim=out_dim)
+        # mixed shapes: broadcast as the reference solvers do (src/qkan/solver/exact.py:68-86)
         if theta.dim() != 4:
             theta = theta.unsqueeze(0)
         if theta.shape[1] != in_dim or theta.shape[0] != out_dim:
@@ -44,7 +53,6 @@ class B200Solver:
             rep_out = out_dim if preacts_weight.shape[0] == 1 else 1
             preacts_weight = preacts_weight.repeat(rep_out, rep_in, 1)[:, :in_dim]
             preacts_bias = preacts_bias.repeat(rep_out, rep_in, 1)[:, :in_dim]
-        layers = reps if ansatz == "real" else reps + 1
         if theta.shape[2] != layers:
             raise ValueError(f"theta holds {theta.shape[2]} layers, reps={reps} needs {layers}")
         return qf.qkan_postacts(x, theta, preacts_weight, preacts_bias, preact_trainable=trainable,

@@ -164,6 +164,49 @@ def ansatz_cases(qkan, torch):
     np.savez_compressed(os.path.join(HERE, "ansatz_cases.npz"), **out)
 
 
+# name, ansatz, B, I, O, R, group, preact_trainable, fast_measure
+GROUP_CASES = [
+    ("group_pz_g3", "pz_encoding", 6, 7, 4, 2, 3, True, True),      # 7 inputs over 3 entries: ragged classes
+    ("group_pz_g1_fixed", "pz_encoding", 5, 4, 3, 3, 1, False, False),
+    ("group_pz_g40_wide", "pz_encoding", 4, 35, 3, 1, 40, True, True),  # more entries than inputs
+    ("group_rpz_g2", "rpz_encoding", 5, 5, 2, 2, 2, False, True),
+    ("group_real_g3", "real", 6, 8, 3, 3, 3, True, True),
+]
+
+
+def group_cases(qkan, torch):
+    """Grouped theta / preacts (g, ...) through the reference solver, which broadcasts them itself."""
+    out = {}
+    solver = qkan.solver.get_solver("exact")
+    for idx, (name, ansatz, B, I, O, R, G, ptr, fast) in enumerate(GROUP_CASES):
+        g = torch.Generator().manual_seed(3000 + idx)
+        rnd = lambda *s: torch.rand(*s, generator=g, dtype=torch.float64)  # noqa: E731
+        nrm = lambda *s: torch.randn(*s, generator=g, dtype=torch.float64)  # noqa: E731
+        leaf = lambda t: t.clone().requires_grad_(True)  # noqa: E731
+        th_shape = {"pz_encoding": (G, R + 1, 2), "rpz_encoding": (G, R + 1, 1), "real": (G, R, 1)}[ansatz]
+        x = leaf(rnd(B, I) * 4 - 2)
+        theta = leaf((rnd(*th_shape) * 2 - 1) * np.pi)
+        pw = leaf(1 + 0.3 * nrm(G, R))
+        pb = leaf(0.3 * nrm(G, R))
+        postw = leaf(nrm(O, I) / np.sqrt(I))
+        postb = leaf(0.5 * nrm(O, I))
+        gy = nrm(B, O)
+        pa = solver(x, theta, pw, pb, R, ansatz=ansatz, preacts_trainable=ptr, fast_measure=fast,
+                    out_dim=O, dtype=torch.float64 if ansatz == "real" else torch.complex128)
+        y = ((pa + postb) * postw).sum(dim=2)
+        (y * gy).sum().backward()
+        zero = lambda t: t.grad if t.grad is not None else torch.zeros_like(t)  # noqa: E731
+        for k, v in dict(in_x=x, in_theta=theta, in_preacts_weight=pw, in_preacts_bias=pb,
+                         in_postact_weights=postw, in_postact_bias=postb, in_gy=gy, y=y, postacts=pa,
+                         g_x=zero(x), g_theta=zero(theta), g_preacts_weight=zero(pw), g_preacts_bias=zero(pb),
+                         g_postact_weights=zero(postw), g_postact_bias=zero(postb)).items():
+            out[f"{name}/{k}"] = v.detach().numpy()
+        out[f"{name}/flags"] = np.array([int(ptr), int(fast)], dtype=np.int64)
+        out[f"{name}/ansatz"] = np.array(ansatz)
+    out["names"] = np.array([c[0] for c in GROUP_CASES])
+    np.savez_compressed(os.path.join(HERE, "group_cases.npz"), **out)
+
+
 def init_cases(qkan, torch):
     out = {}
     specs = {
@@ -220,6 +263,8 @@ def main():
         layer_cases(qkan, torch)
     if only in ("all", "ansatz"):
         ansatz_cases(qkan, torch)
+    if only in ("all", "group"):
+        group_cases(qkan, torch)
     if only in ("all", "init"):
         init_cases(qkan, torch)
     if only in ("all", "fit"):

@@ -28,7 +28,7 @@ def test_library_exports_every_declared_symbol():
 
 def test_descriptor_layout_and_pure_host_queries():
     lib = _abi.load()
-    assert ctypes.sizeof(_abi.QkDesc) == 32
+    assert ctypes.sizeof(_abi.QkDesc) == 36
     assert lib.qk_abi_version() == _abi.QK_ABI_VERSION
     d = _abi.QkDesc(65536, 256, 256, 3, _abi.QK_F32, _abi.QK_F32, 7, 0)
     fwd = lib.qk_forward_workspace_bytes(_abi.desc_pointer(d))

@@ -174,7 +174,7 @@ def test_graphed_train_step_and_inference_match_eager():
     for _ in range(2):  # replays are idempotent
         loss_g = step(x, labels)
         torch.cuda.synchronize()
-        assert abs(float(loss_g) - float(loss_e)) <= 1e-6 * abs(float(loss_e))
+        assert abs(float(loss_g.detach()) - float(loss_e.detach())) <= 1e-6 * abs(float(loss_e.detach()))
         for n, p in model.named_parameters():
             if n in eager:
                 assert nerr(p.grad.cpu().numpy(), eager[n].cpu().numpy()) <= 1e-6, n

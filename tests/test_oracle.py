@@ -3,8 +3,8 @@ import numpy as np
 import pytest
 
 from oracle import oracle
-from tests.util import (GRAD_NAMES, ansatz_case_inputs, case_inputs, golden_ansatz_cases, golden_layer_cases,
-                        nerr)
+from tests.util import (GRAD_NAMES, ansatz_case_inputs, case_inputs, expand_group, golden_ansatz_cases,
+                        golden_group_cases, golden_layer_cases, nerr, reduce_group)
 
 
 @pytest.mark.parametrize("case", golden_layer_cases(), ids=lambda c: c["name"])
@@ -69,3 +69,19 @@ def test_oracle_matches_reference_for_rpz_and_real(case):
     g = oracle.backward(*args, p["gy"], **cfg)
     for k in GRAD_NAMES:
         assert nerr(g[k], case["g_" + k]) <= 1e-12, k
+
+
+@pytest.mark.parametrize("case", golden_group_cases(), ids=lambda c: c["name"])
+def test_oracle_with_group_broadcast_matches_reference(case):
+    """Pins the grouping rule (entry i mod g for every output) on the reference's own broadcast."""
+    cfg = case["cfg"]
+    O, I = case["in_postact_weights"].shape
+    G = case["in_theta"].shape[0]
+    theta, pw, pb = (expand_group(case[k], O, I) for k in ("in_theta", "in_preacts_weight", "in_preacts_bias"))
+    args = [case["in_x"], theta, pw, pb, case["in_postact_weights"], case["in_postact_bias"], None, None]
+    assert nerr(oracle.forward(*args, **cfg), case["y"]) <= 1e-13
+    g = oracle.backward(*args, case["in_gy"], **cfg)
+    for k in ("x", "postact_weights", "postact_bias"):
+        assert nerr(g[k], case["g_" + k]) <= 1e-12, k
+    for k in ("theta", "preacts_weight", "preacts_bias"):
+        assert nerr(reduce_group(g[k], G), case["g_" + k]) <= 1e-12, k

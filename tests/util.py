@@ -89,3 +89,31 @@ def ansatz_case_inputs(g):
     return dict(x=g["in_x"], theta=g["in_theta"], pw=g["in_preacts_weight"], pb=g["in_preacts_bias"],
                 postw=g["in_postact_weights"], postb=g["in_postact_bias"], basew=g["in_base_weight"],
                 mask=g["in_mask"], gy=g["in_gy"])
+
+
+def golden_group_cases():
+    """Grouped theta / preacts ``(g, ...)`` run through the reference's exact solver (float64 / complex128)."""
+    d = np.load(os.path.join(GOLDEN, "group_cases.npz"))
+    cases = []
+    for name in d["names"]:
+        name = str(name)
+        g = {k.split("/", 1)[1]: d[k] for k in d.files if k.startswith(name + "/")}
+        ptr, fast = (bool(v) for v in g["flags"])
+        g["cfg"] = dict(preact_trainable=ptr, fast_measure=fast, use_postact_bias=True, ansatz=str(g["ansatz"]))
+        g["name"] = name
+        cases.append(g)
+    return cases
+
+
+def expand_group(t, out_dim: int, in_dim: int):
+    """(g, ...) -> (O, I, ...) with entry ``i mod g`` on edge (o, i): the broadcast the reference solvers apply."""
+    idx = np.arange(in_dim) % t.shape[0]
+    return np.broadcast_to(t[idx][None], (out_dim, in_dim) + t.shape[1:]).copy()
+
+
+def reduce_group(g_edge, group: int):
+    """Sum per-edge gradients (O, I, ...) over the edges sharing an entry -> (g, ...)."""
+    out = np.zeros((group,) + g_edge.shape[2:], dtype=g_edge.dtype)
+    for i in range(g_edge.shape[1]):
+        out[i % group] += g_edge[:, i].sum(axis=0)
+    return out
