@@ -65,9 +65,13 @@ def _jobs():
     return jobs
 
 
-def _compile(job, extra) -> str:
+def _compile(job, extra, force: bool = False) -> str:
     src, stem, defs = job
     obj = os.path.join(OBJ, stem + ".o")
+    if not force and not extra and os.path.exists(obj):  # object newer than its source and every header: keep it
+        headers = glob.glob(os.path.join(CSRC, "*.cuh")) + glob.glob(os.path.join(INCLUDE, "*.h"))
+        if os.path.getmtime(obj) > max(os.path.getmtime(p) for p in [src, __file__, *headers]):
+            return obj
     cmd = [_nvcc(), *NVCC_FLAGS, *defs, *extra, "-c", src, "-o", obj]
     res = subprocess.run(cmd, capture_output=True, text=True)
     log = os.path.join(OBJ, stem + ".ptxas.log")
@@ -84,7 +88,7 @@ def build(force: bool = False, extra_flags=()) -> str:
         return LIB
     os.makedirs(OBJ, exist_ok=True)
     with cf.ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 1)) as pool:
-        objs = list(pool.map(lambda j: _compile(j, list(extra_flags)), _jobs()))
+        objs = list(pool.map(lambda j: _compile(j, list(extra_flags), force), _jobs()))
     res = subprocess.run([_nvcc(), "-shared", "-o", LIB, *objs, "-gencode",
                           "arch=compute_100a,code=sm_100a"], capture_output=True, text=True)
     if res.returncode != 0:

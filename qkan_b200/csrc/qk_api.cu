@@ -58,6 +58,7 @@ struct Layout {
     int ipad;
     size_t table_off, bias_off, colsum_off, partials_off, total;
     size_t gtheta_off, gpw_off, gpb_off;  // per-edge gradients ahead of the group reduction (group > 0)
+    size_t gxpart_off;                    // grad_x shares of the output slices (BwdCfg::osplit > 1)
     int ncolsplit;
 };
 
@@ -85,6 +86,10 @@ Layout backward_layout(const QkDesc& d, bool base) {
     l.partials_off = l.colsum_off + qk::align256((size_t)l.ncolsplit * d.out_dim * sizeof(float));
     l.total = l.partials_off +
               qk::align256((size_t)c.grid_b * d.out_dim * c.nacc * l.ipad * sizeof(float));
+    if (c.osplit > 1) {
+        l.gxpart_off = l.total;
+        l.total += qk::align256((size_t)c.osplit * d.batch * d.in_dim * sizeof(float));
+    }
     if (d.group > 0) {
         const size_t nE = (size_t)d.out_dim * d.in_dim;
         l.gtheta_off = l.total;
@@ -247,17 +252,22 @@ int run_backward(const QkDesc* desc, const void* x, const float* theta, const fl
     b.precise = (d.flags & QK_PRECISE_MATH) != 0;
     b.cfg = qk::choose_bwd_cfg(d, has_base);
     if (getenv("QK_DEBUG"))
-        fprintf(stderr, "[qk] backward B=%d I=%d O=%d R=%d: %d groups x %d rows, grid %d x %d, smem %zu, ru %d\n",
+        fprintf(stderr, "[qk] backward B=%d I=%d O=%d R=%d: %d groups x %d rows, grid %d x %d x %d output slices of %d, smem %zu, ru %d\n",
                 d.batch, d.in_dim, d.out_dim, d.reps, b.cfg.groups, b.cfg.rpg, b.cfg.grid_b, b.cfg.grid_i,
-                b.cfg.smem, b.cfg.ru);
+                b.cfg.osplit, b.cfg.ochunk, b.cfg.smem, b.cfg.ru);
     b.x = x;
     b.gy = gy;
     b.gpostacts = gpostacts;
     b.table = p.table;
     b.gx = gx;
+    b.gx_part = b.cfg.osplit > 1 ? reinterpret_cast<float*>(wsb + l.gxpart_off) : nullptr;
     b.partials = reinterpret_cast<float*>(wsb + l.partials_off);
     e = qk::launch_backward(b, p.rk, (d.flags & QK_FAST_MEASURE) != 0, d.io_dtype, has_base, st);
     if (e != cudaSuccess) return cuda_fail(e, "backward launch");
+    if (gx && b.cfg.osplit > 1) {
+        e = qk::launch_sum_gx(b.gx_part, gx, d.io_dtype, (size_t)d.batch * d.in_dim, b.cfg.osplit, st);
+        if (e != cudaSuccess) return cuda_fail(e, "grad_x slice sum launch");
+    }
 
     if (gtheta || gpw || gpb || gpostw || gpostb || gbasew) {
         qk::FinishArgs f{};

@@ -100,7 +100,7 @@ __device__ __forceinline__ float edge_backward(const EdgeFwd<R>& e, float bw, fl
 
 constexpr int kGyChunk = 8;  // outputs whose grad_y columns are staged together
 
-template <int R, bool FAST, typename IO, bool BASE, bool EDGES, int RU, bool PRECISE>
+template <int R, bool FAST, typename IO, bool BASE, bool EDGES, int RU, bool PRECISE, bool OSLICE>
 __global__ void __launch_bounds__(256) backward_kernel(BwdArgs a) {
     constexpr int NACC = acc_rows(R, BASE);
     // floats per tile row: 32 (x, grad_x) pairs [+ 32 (silu, silu') pairs]; a pair is one 64-bit access
@@ -133,8 +133,13 @@ __global__ void __launch_bounds__(256) backward_kernel(BwdArgs a) {
     }
     // a thread only ever touches its own column of its own group's rows: no barrier needed for xg_s
 
-    for (int oc = 0; oc < a.out_dim; oc += kGyChunk) {
-        const int nch = min(kGyChunk, a.out_dim - oc);
+    // OSLICE: blockIdx.z selects a slice of the outputs (small batches: more CTAs in flight; see
+    // BwdCfg::osplit). A separate instantiation, so that the unsliced kernel keeps its bound in the
+    // constant bank instead of a register.
+    const int o_begin = OSLICE ? blockIdx.z * a.cfg.ochunk : 0;
+    const int o_end = OSLICE ? min(a.out_dim, o_begin + a.cfg.ochunk) : a.out_dim;
+    for (int oc = o_begin; oc < o_end; oc += kGyChunk) {
+        const int nch = min(kGyChunk, o_end - oc);
         if (!EDGES) {
             // stage grad_y[b0 .. b0+tb, oc .. oc+nch) transposed; rows past the batch read as 0
             if (std::is_same<IO, float>::value && nch == kGyChunk && (a.out_dim & 3) == 0 &&
@@ -235,7 +240,14 @@ __global__ void __launch_bounds__(256) backward_kernel(BwdArgs a) {
         }
     }
 
-    if (a.gx) {
+    if (OSLICE && a.gx) {
+        // this output slice's share of grad_x; sum_gx_kernel adds the slices in order
+        float* __restrict__ gxp = a.gx_part + (size_t)blockIdx.z * a.batch * a.in_dim;
+        for (int j = 0; j < rpg; ++j) {
+            const int row = row0 + j;
+            if (b0 + row < a.batch && i < a.in_dim) gxp[(size_t)(b0 + row) * a.in_dim + i] = my[j * ROW + 1];
+        }
+    } else if (!OSLICE && a.gx) {
         IO* __restrict__ gx = static_cast<IO*>(a.gx);
         for (int j = 0; j < rpg; ++j) {
             const int row = row0 + j;
@@ -247,15 +259,23 @@ __global__ void __launch_bounds__(256) backward_kernel(BwdArgs a) {
 
 template <int R, bool FAST, typename IO, bool BASE, bool EDGES>
 static cudaError_t launch_bwd_t(const BwdArgs& a, cudaStream_t st) {
-    auto kern = a.cfg.ru == 4 ? backward_kernel<R, FAST, IO, BASE, EDGES, 4, false>
-                              : backward_kernel<R, FAST, IO, BASE, EDGES, 2, false>;
+    auto kern = a.cfg.ru == 4 ? backward_kernel<R, FAST, IO, BASE, EDGES, 4, false, false>
+                              : backward_kernel<R, FAST, IO, BASE, EDGES, 2, false, false>;
     if constexpr (std::is_same<IO, float>::value) {  // the full-precision variant exists for float32 I/O
-        if (a.precise) kern = backward_kernel<R, FAST, IO, BASE, EDGES, 2, true>;
+        if (a.precise) kern = backward_kernel<R, FAST, IO, BASE, EDGES, 2, true, false>;
+    }
+    if (a.cfg.osplit > 1) {
+        // sliced outputs: one row-interleave per repetition count (rows per group are multiples of 4)
+        constexpr int RU_S = (R > 8) ? 2 : 4;
+        kern = backward_kernel<R, FAST, IO, BASE, EDGES, RU_S, false, true>;
+        if constexpr (std::is_same<IO, float>::value) {
+            if (a.precise) kern = backward_kernel<R, FAST, IO, BASE, EDGES, 2, true, true>;
+        }
     }
     cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            (int)a.cfg.smem);
     if (err != cudaSuccess) return err;
-    dim3 grid(a.cfg.grid_b, a.cfg.grid_i);
+    dim3 grid(a.cfg.grid_b, a.cfg.grid_i, a.cfg.osplit);
     kern<<<grid, a.cfg.groups * kWarp, a.cfg.smem, st>>>(a);
     return cudaPeekAtLastError();
 }

@@ -74,10 +74,17 @@ BwdCfg choose_bwd_cfg(const QkDesc& d, bool base) {
         const int tb = groups * rpg;
         size_t smem = (size_t)tb * 32 * 4 * (base ? 4 : 2) + (size_t)kGyChunkHost * tb * 4 +
                       (size_t)2 * groups * nacc * 32 * 4;
-        return BwdCfg{groups, rpg, tb, (d.batch + tb - 1) / tb, grid_i, nacc, smem, ru};
+        return BwdCfg{groups, rpg, tb, (d.batch + tb - 1) / tb, grid_i, nacc, smem, ru, 1, round_up(d.out_dim, kGyChunkHost)};
+    };
+    auto slice = [&](BwdCfg c, int want) {  // cut the outputs into about `want` slices of a multiple of 8
+        c.ochunk = round_up((d.out_dim + want - 1) / want, kGyChunkHost);
+        c.osplit = (d.out_dim + c.ochunk - 1) / c.ochunk;
+        return c;
     };
     const int force_groups = tune_int("QK_BWD_GROUPS", 0), force_rpg = tune_int("QK_BWD_RPG", 0);
-    if (force_groups > 0 && force_rpg > 0) return make(force_groups, force_rpg);  // developer override
+    const int force_osplit = tune_int("QK_BWD_OSPLIT", 0);
+    if (force_groups > 0 && force_rpg > 0)  // developer override
+        return slice(make(force_groups, force_rpg), force_osplit > 0 ? force_osplit : 1);
     // (row groups = warps per CTA, rows per group), largest tile first
     static const int cand[][2] = {{8, 32}, {8, 16}, {4, 32}, {4, 16}, {8, 8}, {2, 32}, {4, 8}, {2, 16}, {2, 8}, {1, 8}};
     const int regs_est = rk > 8 ? 255 : 34 + 11 * rk;
@@ -108,6 +115,44 @@ BwdCfg choose_bwd_cfg(const QkDesc& d, bool base) {
             const double compute = (double)per_sm * cur.tb * d.out_dim * t_unit * setup * occupancy * small_cta;
             const double partials = 2.0 * partial_bytes / 6.0e12;  // written here, read by finish_grads
             const double cost = compute + partials;
+            if (best_cost < 0 || cost < best_cost * 0.999) {
+                best = cur;
+                best_cost = cost;
+            }
+        }
+    }
+    if (force_osplit > 0) return slice(best, force_osplit);
+    // Small batches: the choice above leaves fewer than 16 warps per SM, and a CTA's time is then the
+    // dependent chain of one output after the other (constant load, rows, reduction), not issue slots.
+    // Smaller tiles and output slices put more chains in flight. Per output a warp spends about
+    // 0.8 us + its rows x 0.175 us (measured at 3 repetitions, scaled by the instruction count).
+    if ((long)best.grid_b * grid_i * best.groups >= kSmCount * 16 || d.batch <= 0) return best;
+    static const int small[][2] = {{8, 16}, {8, 8}, {4, 8}, {8, 4}, {4, 4}, {2, 8}, {2, 4}};
+    const double chain0 = 0.8e-6, chain_row = 0.175e-6 * (28.0 * rk + 20.0) / 104.0;
+    best_cost = -1.0;
+    for (auto& c : small) {
+        if (c[1] % ru) continue;
+        for (int want = 1; want <= 64; want *= 2) {
+            if (want > 1 && d.out_dim < 32) break;  // too few outputs to be worth a second pass over grad_x
+            BwdCfg cur = slice(make(c[0], c[1]), want);
+            if (cur.osplit < want && want > 1 && cur.osplit <= want / 2) continue;  // same slicing as a smaller `want`
+            long resident = (long)(kSmemPerSm / (cur.smem + 1024));
+            const long by_regs = 65536 / ((long)regs_est * cur.groups * 32);
+            if (by_regs < resident) resident = by_regs;
+            if (resident > 32) resident = 32;
+            if (resident < 1) resident = 1;
+            const long ctas = (long)cur.grid_b * grid_i * cur.osplit;
+            const long per_sm = (ctas + kSmCount - 1) / kSmCount;
+            const long live = per_sm < resident ? per_sm : resident;
+            const long waves = (per_sm + resident - 1) / resident;
+            const double setup = 1.0 + 0.09 * 32.0 / cur.rpg;
+            const double issue = (double)live * cur.tb * t_unit * setup;   // the SM's issue slots shared by its CTAs
+            const double chain = chain0 + cur.rpg * chain_row;
+            const double per_output = issue > chain ? issue : chain;
+            const double partial_bytes = (double)cur.grid_b * d.out_dim * nacc * ipad * 4.0;
+            const double gx_bytes = cur.osplit > 1 ? (double)(cur.osplit + 1) * d.batch * d.in_dim * 4.0 : 0.0;
+            const double cost = (double)waves * cur.ochunk * per_output + (2.0 * partial_bytes + gx_bytes) / 3.0e12 +
+                                (cur.osplit > 1 ? 4.0e-6 : 0.0);  // + the launch that adds the grad_x shares
             if (best_cost < 0 || cost < best_cost * 0.999) {
                 best = cur;
                 best_cost = cost;

@@ -58,6 +58,10 @@ struct BwdCfg {
     int nacc;
     size_t smem;
     int ru;  // rows a thread interleaves in its inner loop (2 or 4)
+    // Small batches leave most SMs idle when a CTA walks all outputs, so the outputs are cut into
+    // `osplit` slices of `ochunk` (a multiple of 8) handled by different CTAs (grid.z). Each slice writes
+    // its share of grad_x to scratch and sum_gx adds the shares in order.
+    int osplit, ochunk;
 };
 
 struct FwdArgs {
@@ -81,6 +85,7 @@ struct BwdArgs {
     const void* gpostacts;  // (B,O,I) solver-contract mode (gy unused)
     const float* table;
     void* gx;  // may be nullptr
+    float* gx_part;  // [osplit][B][I] float scratch, used when cfg.osplit > 1
     float* partials;
 };
 
@@ -91,6 +96,8 @@ cudaError_t launch_prep(const PrepArgs& a, cudaStream_t st);
 cudaError_t launch_colsum(const void* gy, int io_dtype, int B, int O, int nsplit, float* part,
                           cudaStream_t st);
 cudaError_t launch_finish(const FinishArgs& a, cudaStream_t st);
+// gx[n] = sum over the output slices of part[s][n], in slice order, stored in the I/O dtype
+cudaError_t launch_sum_gx(const float* part, void* gx, int io_dtype, size_t n, int nslices, cudaStream_t st);
 // dst[k*per + c] = sum over o and over i == k (mod group) of src[(o*in_dim + i)*per + c], fixed order
 cudaError_t launch_group_reduce(const float* src, float* dst, int out_dim, int in_dim, int group, int per,
                                 cudaStream_t st);

@@ -129,21 +129,32 @@ __global__ void colsum_kernel(const IO* __restrict__ gy, int B, int O, int nspli
     }
 }
 
+// Block = 32 input columns (one lane each) x `blockDim.y` tile slices. Every slice adds the per-tile
+// partials t = slice, slice + slices, ... of each accumulator row; slice 0 then adds the slice sums in
+// order and writes the gradients. Fixed order throughout: run-to-run bitwise reproducible.
 __global__ void finish_grads_kernel(FinishArgs a) {
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    extern __shared__ float part[];  // [slices][nacc][32]
+    const int lane = threadIdx.x, slice = threadIdx.y, slices = blockDim.y;
+    const int i = blockIdx.x * kWarp + lane;  // < ipad
     const int o = blockIdx.y;
-    if (i >= a.in_dim) return;
     const int R = a.reps, RK = a.rk;
     const int nacc = a.nacc;
+    const size_t tile_stride = (size_t)a.out_dim * nacc * a.ipad;
+    const float* p0 = a.partials + ((size_t)o * nacc) * a.ipad + i;
+    for (int k = 0; k < nacc; ++k) {
+        const float* p = p0 + (size_t)k * a.ipad;
+        float s = 0.f;
+        for (int t = slice; t < a.ntiles; t += slices) s += p[(size_t)t * tile_stride];
+        part[(slice * nacc + k) * kWarp + lane] = s;
+    }
+    __syncthreads();
+    if (slice != 0 || i >= a.in_dim) return;
     const size_t e = (size_t)o * a.in_dim + i;
     const bool ptr = (a.flags & QK_PREACT_TRAINABLE) != 0 || a.ansatz == QK_ANSATZ_RPZ;
     const bool use_pb = (a.flags & QK_USE_POSTACT_BIAS) != 0 && a.postb != nullptr;
-    const size_t tile_stride = (size_t)a.out_dim * nacc * a.ipad;
-    const float* p0 = a.partials + ((size_t)o * nacc) * a.ipad + i;
     auto total = [&](int k) {
         float s = 0.f;
-        const float* p = p0 + (size_t)k * a.ipad;
-        for (int t = 0; t < a.ntiles; ++t) s += p[(size_t)t * tile_stride];
+        for (int w = 0; w < slices; ++w) s += part[(w * nacc + k) * kWarp + lane];
         return s;
     };
     if (a.ansatz == QK_ANSATZ_REAL) {
@@ -224,6 +235,24 @@ cudaError_t launch_group_reduce(const float* src, float* dst, int out_dim, int i
     return cudaPeekAtLastError();
 }
 
+template <typename IO>
+__global__ void sum_gx_kernel(const float* __restrict__ part, IO* __restrict__ gx, size_t n, int nslices) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n) return;
+    float s = 0.f;
+    for (int z = 0; z < nslices; ++z) s += part[(size_t)z * n + idx];
+    st_from_float(gx + idx, s);
+}
+
+cudaError_t launch_sum_gx(const float* part, void* gx, int io_dtype, size_t n, int nslices, cudaStream_t st) {
+    const unsigned blocks = (unsigned)((n + 255) / 256);
+    if (io_dtype == QK_BF16)
+        sum_gx_kernel<<<blocks, 256, 0, st>>>(part, static_cast<__nv_bfloat16*>(gx), n, nslices);
+    else
+        sum_gx_kernel<<<blocks, 256, 0, st>>>(part, static_cast<float*>(gx), n, nslices);
+    return cudaPeekAtLastError();
+}
+
 cudaError_t launch_prep(const PrepArgs& a, cudaStream_t st) {
     dim3 grid((a.ipad + 127) / 128, a.out_dim);
     prep_table_kernel<<<grid, 128, 0, st>>>(a);
@@ -242,8 +271,12 @@ cudaError_t launch_colsum(const void* gy, int io_dtype, int B, int O, int nsplit
 }
 
 cudaError_t launch_finish(const FinishArgs& a, cudaStream_t st) {
-    dim3 grid((a.in_dim + 127) / 128, a.out_dim);
-    finish_grads_kernel<<<grid, 128, 0, st>>>(a);
+    // as many tile slices as there are tiles to share out, within 48 KB of shared memory
+    int slices = 8;
+    while (slices > 1 && (slices / 2 >= a.ntiles || (size_t)slices * a.nacc * kWarp * sizeof(float) > 48 * 1024))
+        slices /= 2;
+    dim3 grid(a.ipad / kWarp, a.out_dim), block(kWarp, slices);
+    finish_grads_kernel<<<grid, block, (size_t)slices * a.nacc * kWarp * sizeof(float), st>>>(a);
     return cudaPeekAtLastError();
 }
 

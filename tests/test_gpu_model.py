@@ -243,3 +243,33 @@ def test_refine_is_function_preserving(ansatz):
     bigger = model.refine(5)
     assert bigger.layers[0].reps == 5 and bigger.layers[0].theta.shape[2] == 6
     assert nerr(bigger(x).detach().cpu().numpy(), model(x).detach().cpu().numpy()) <= 1e-6
+
+
+@pytest.mark.parametrize("ansatz", ["pz_encoding", "real"])
+def test_hybrid_block_bf16_eager_and_graphed(ansatz):
+    """Linear -> QKAN -> Linear block in bfloat16: matches a float32 twin, and the captured step matches eager."""
+    from qkan_b200 import FusedHQKAN
+    from qkan_b200.graph import make_graphed_train_step
+
+    torch.manual_seed(0)
+    block = FusedHQKAN(48, 16, reps=2, ansatz=ansatz)
+    assert block.qkan.layers[0].solver == "b200" and block.down.weight.dtype == torch.bfloat16
+    x = (torch.rand(4, 32, 48, device="cuda") * 2 - 1).to(torch.bfloat16)
+    y = block(x.view(-1, 48))
+    twin = FusedHQKAN(48, 16, reps=2, ansatz=ansatz, p_dtype=torch.float32, c_dtype=torch.float32)
+    twin.load_state_dict({k: v.float() for k, v in block.state_dict().items()})
+    y32 = twin(x.view(-1, 48).float())
+    assert nerr(y.detach().float().cpu().numpy(), y32.detach().cpu().numpy()) <= 2 * TOL_BF16
+    target = torch.randn_like(y)
+    loss_fn = lambda out, t: (out.float() - t.float()).square().mean()  # noqa: E731
+    loss_e = loss_fn(block(x.view(-1, 48)), target)
+    loss_e.backward()
+    eager = {n: p.grad.clone() for n, p in block.named_parameters() if p.grad is not None}
+    assert "qkan.layers.0.theta" in eager and "down.weight" in eager
+    step = make_graphed_train_step(block, x.view(-1, 48), target, loss_fn, torch.optim.SGD(block.parameters(), lr=0.0))
+    loss_g = step(x.view(-1, 48), target)
+    torch.cuda.synchronize()
+    assert abs(float(loss_g.detach()) - float(loss_e.detach())) <= 1e-3 * abs(float(loss_e.detach()))
+    for n, p in block.named_parameters():
+        if n in eager:
+            assert nerr(p.grad.float().cpu().numpy(), eager[n].float().cpu().numpy()) <= 1e-6, n
