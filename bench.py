@@ -47,10 +47,10 @@ def work_per_edge(reps: int):
 SM_COUNT, FP32_LANES, SFU_LANES, NOMINAL_GHZ = 148, 128, 16, 1.965
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one backward_kernel launch, from the ncu capture of a
-# 16384-row case (52.1 MB + 162.3 MB, same backward tile as the full batch) scaled by 4 to the 65536-row
+# 16384-row case (53.7 MB + 162.8 MB, backward tile pinned to the full batch's) scaled by 4 to the 65536-row
 # batch; the traffic is proportional to the batch (activations and per-tile partials).
 # See profiles/forward_backward_kernels_batch16384.md.
-BACKWARD_DRAM_BYTES_PER_LAUNCH = 4 * (52_137_216 + 162_258_688)
+BACKWARD_DRAM_BYTES_PER_LAUNCH = 4 * (53_745_664 + 162_844_672)
 
 
 def issue_roofline_seconds(edges: float, reps: int, which: str, ghz: float = NOMINAL_GHZ) -> float:
