@@ -306,6 +306,8 @@ def run_b200(args):
     e0.record()
     for _ in range(e2e_steps):
         e2e_step()
+    if pipe is not None:
+        pipe.wait()  # the last step's copy-out belongs to the timed region
     e1.record()
     sync_all()
     e2e_ms = e0.elapsed_time(e1) / e2e_steps if e2e_steps else float("nan")

@@ -12,6 +12,11 @@ kernels: the batch is cut into row chunks, and three streams run as a pipeline â
 Rows are independent, so chunking changes nothing but the order in which the batch-summed
 parameter gradients are accumulated (chunk partial sums are added in chunk order: still
 run-to-run reproducible).
+
+Chunk boundaries sit on multiples of ``row_align`` rows (default: 148 SMs x 64 rows, one full wave of
+forward tiles and, at 256 columns, of backward tiles), so that cutting the batch does not add partly
+filled waves of CTAs. Successive steps overlap too: the copy-out of one step's last chunk runs under the
+next step's first kernels (``wait()`` orders the current stream after everything queued so far).
 """
 from __future__ import annotations
 
@@ -28,12 +33,15 @@ class HostLayerPipeline:
 
     def __init__(self, batch: int, in_dim: int, out_dim: int, reps: int, device, *, n_chunks: int = 4,
                  dtype: torch.dtype = torch.float32, preact_trainable: bool = True,
-                 fast_measure: bool = True, use_postact_bias: bool = True, ansatz: str = "pz_encoding"):
+                 fast_measure: bool = True, use_postact_bias: bool = True, ansatz: str = "pz_encoding",
+                 row_align: int = 148 * 64):
         self.device = torch.device(device)
         self.cfg = dict(preact_trainable=preact_trainable, fast_measure=fast_measure,
                         use_postact_bias=use_postact_bias, ansatz=ansatz)
         n_chunks = max(1, min(n_chunks, batch))
         step = (batch + n_chunks - 1) // n_chunks
+        if row_align > 1 and batch >= 2 * row_align:  # whole waves per chunk; the last chunk takes the remainder
+            step = max(row_align, (step + row_align // 2) // row_align * row_align)
         self.spans = [(b, min(batch, b + step)) for b in range(0, batch, step)]
         dev = self.device
         self.dx = [torch.empty((e - b, in_dim), dtype=dtype, device=dev) for b, e in self.spans]
@@ -52,13 +60,16 @@ class HostLayerPipeline:
         self.ev_in = [torch.cuda.Event() for _ in self.spans]
         self.ev_done = [torch.cuda.Event() for _ in self.spans]
         self.ev_free = [torch.cuda.Event() for _ in self.spans]    # chunk buffers drained by copy-out
+        self.ev_sum = torch.cuda.Event()                            # summed gradients ready
+        self.ev_sum_free = torch.cuda.Event()                       # ... and copied out
         self._first = True
 
     def step(self, hx: torch.Tensor, hgy: torch.Tensor, params: Dict[str, Optional[torch.Tensor]],
              hy: torch.Tensor, hgx: torch.Tensor, hgrads: Optional[torch.Tensor] = None) -> GradBucket:
         """Queue one forward+backward. ``hx, hgy, hy, hgx, hgrads`` are pinned host tensors; ``params`` holds the
-        device tensors theta, pw, pb, postw, postb (basew / mask optional). Returns the gradient bucket; the
-        caller synchronises (``torch.cuda.synchronize()`` or an event on the current stream) before reading."""
+        device tensors theta, pw, pb, postw, postb (basew / mask optional). Returns the gradient bucket
+        (device; valid for work queued on the current stream). Host results are complete after ``wait()`` plus a
+        synchronisation of the current stream, or after ``torch.cuda.synchronize()``."""
         compute = torch.cuda.current_stream(self.device)
         p = params
         for k, (b, e) in enumerate(self.spans):
@@ -69,6 +80,8 @@ class HostLayerPipeline:
                 self.dgy[k].copy_(hgy[b:e], non_blocking=True)
                 self.ev_in[k].record(self.s_in)
             compute.wait_event(self.ev_in[k])
+            if not self._first:
+                compute.wait_event(self.ev_free[k])  # the previous step's grad_x of this chunk has left the device
             y = qf.layer_forward(self.dx[k], p["theta"], p["pw"], p["pb"], p["postw"], p.get("postb"),
                                  p.get("basew"), p.get("mask"), **self.cfg)
             outs = dict(self.chunk_buckets[k].views, x=self.dgx[k])
@@ -82,13 +95,22 @@ class HostLayerPipeline:
                 hgx[b:e].copy_(self.dgx[k], non_blocking=True)
                 self.ev_free[k].record(self.s_out)
             y.record_stream(self.s_out)
-        self._first = False
         flat = self.bucket.flat
+        if not self._first:
+            compute.wait_event(self.ev_sum_free)  # the previous step's gradients have left the device
+        self._first = False
         flat.copy_(self.chunk_buckets[0].flat)
         for cb in self.chunk_buckets[1:]:
             flat.add_(cb.flat)
         self.bucket.all_reduce()
-        if hgrads is not None:
-            hgrads.copy_(flat, non_blocking=True)
-        compute.wait_stream(self.s_out)
+        self.ev_sum.record(compute)
+        with torch.cuda.stream(self.s_out):
+            self.s_out.wait_event(self.ev_sum)
+            if hgrads is not None:
+                hgrads.copy_(flat, non_blocking=True)
+            self.ev_sum_free.record(self.s_out)
         return self.bucket
+
+    def wait(self) -> None:
+        """Order the current stream after every copy queued so far (host results are then one stream sync away)."""
+        torch.cuda.current_stream(self.device).wait_stream(self.s_out)

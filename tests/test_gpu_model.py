@@ -155,6 +155,19 @@ def test_host_pipeline_matches_the_direct_call():
         assert nerr(hgx.numpy(), g_ref["x"].cpu().numpy()) <= 1e-6
         for name in ("theta", "preacts_weight", "preacts_bias", "postact_weights", "postact_bias"):
             assert nerr(bucket[name].cpu().numpy(), g_ref[name].cpu().numpy()) <= 2e-6, name
+    # back-to-back steps without a synchronisation in between (copy-out of one step under the next step's
+    # kernels), chunk boundaries on multiples of 256 rows, gradients copied to the host as well
+    pipe = HostLayerPipeline(B, I, O, R, "cuda:0", n_chunks=3, row_align=256)
+    assert [e - b for b, e in pipe.spans] == [256, 256, 256, 232]
+    hgrads = torch.empty(pipe.bucket.flat.numel()).pin_memory()
+    hy.zero_(), hgx.zero_()
+    for _ in range(4):
+        bucket = pipe.step(hx, hgy, dev, hy, hgx, hgrads)
+    pipe.wait()
+    torch.cuda.current_stream().synchronize()
+    assert nerr(hy.numpy(), y_ref.cpu().numpy()) <= 1e-6
+    assert nerr(hgx.numpy(), g_ref["x"].cpu().numpy()) <= 1e-6
+    assert nerr(hgrads.numpy(), bucket.flat.cpu().numpy()) == 0.0
 
 
 def test_graphed_train_step_and_inference_match_eager():
