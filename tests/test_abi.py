@@ -39,6 +39,16 @@ def test_descriptor_layout_and_pure_host_queries():
     assert lib.qk_forward_workspace_bytes(_abi.desc_pointer(bad)) == 0
     assert b"reps" in lib.qk_last_error()
     assert lib.qk_noalloc_max_scratch_bytes() == 8 << 20
+    # grouped parameters add the per-edge gradient scratch ahead of the group reduction
+    g = _abi.QkDesc(65536, 256, 256, 3, _abi.QK_F32, _abi.QK_F32, 7, 0, 3)
+    extra = lib.qk_backward_workspace_bytes(_abi.desc_pointer(g)) - bwd
+    assert extra == 256 * 256 * (8 + 3 + 3) * 4
+    assert lib.qk_forward_workspace_bytes(_abi.desc_pointer(g)) == fwd
+    neg = _abi.QkDesc(4, 4, 4, 1, 0, 0, 0, 0, -1)
+    assert lib.qk_backward_workspace_bytes(_abi.desc_pointer(neg)) == 0 and b"group" in lib.qk_last_error()
+    # a small batch is cut into output slices: room for the slices' grad_x shares is part of the answer
+    small = _abi.QkDesc(256, 256, 256, 3, _abi.QK_F32, _abi.QK_F32, 7, 0)
+    assert lib.qk_backward_workspace_bytes(_abi.desc_pointer(small)) > 2 * 256 * 256 * 4
 
 
 def test_source_tree_never_routes_the_product_through_the_oracle():
