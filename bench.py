@@ -40,8 +40,17 @@ UNIT = "edge-reps/s"
 
 # Algorithmic work per edge-evaluation (pz ansatz, trainable preacts, fast readout):
 # FP32 lane-ops W_f and special-function ops W_m, forward and forward+backward.
-def work_per_edge(reps: int):
+def work_per_edge(reps: int, frozen: bool = False):
+    """Pinned (FP32 lane-ops, SFU ops) per edge evaluation; `frozen` = preacts not trainable (data trig hoisted)."""
+    if frozen:
+        return {"fwd": (12 * reps + 10, 2), "fwd_bwd": (47 * reps + 44, 5)}
     return {"fwd": (11 * reps + 10, 2 * reps + 2), "fwd_bwd": (46 * reps + 44, 4 * reps + 5)}
+
+
+VARIANTS = {"headline": "preacts trainable, fast readout, base term off",
+            "base": "base term on (silu(x) @ base_weight, trainable)",
+            "born": "Born readout (fast_measure=False)",
+            "frozen": "preacts frozen (preact_trainable=False)"}
 
 
 SM_COUNT, FP32_LANES, SFU_LANES, NOMINAL_GHZ = 148, 128, 16, 1.965
@@ -53,8 +62,9 @@ SM_COUNT, FP32_LANES, SFU_LANES, NOMINAL_GHZ = 148, 128, 16, 1.965
 BACKWARD_DRAM_BYTES_PER_LAUNCH = 4 * (53_745_664 + 162_844_672)
 
 
-def issue_roofline_seconds(edges: float, reps: int, which: str, ghz: float = NOMINAL_GHZ) -> float:
-    wf, wm = work_per_edge(reps)[which]
+def issue_roofline_seconds(edges: float, reps: int, which: str, ghz: float = NOMINAL_GHZ,
+                           frozen: bool = False) -> float:
+    wf, wm = work_per_edge(reps, frozen)[which]
     per_edge_clk = max((wf + wm) / FP32_LANES, wm / SFU_LANES)
     return edges * per_edge_clk / (SM_COUNT * ghz * 1e9)
 
@@ -225,16 +235,25 @@ def run_b200(args):
     for k in ("theta", "pw", "pb", "postw", "postb"):
         host[k] = shared[k]
     t = {k: torch.from_numpy(v).to(dev) for k, v in host.items()}
-    cfg = dict(preact_trainable=True, fast_measure=True, use_postact_bias=True)
-    bucket = GradBucket(layer_grad_shapes(IN_DIM, OUT_DIM, REPS), dev)
+    # the headline is the default; the other variants are the extra rows the microbenchmark names
+    # (base term on, Born readout, frozen preacts) and skip the host-buffer and CPU legs
+    variant = args.variant
+    cfg = dict(preact_trainable=variant != "frozen", fast_measure=variant != "born", use_postact_bias=True)
+    basew = None
+    if variant == "base":
+        basew = (0.5 * torch.randn(OUT_DIM, IN_DIM, generator=torch.Generator().manual_seed(5))).to(dev)
+    if variant != "headline":
+        args.no_e2e = args.no_cpu_baseline = True
+    bucket = GradBucket(layer_grad_shapes(IN_DIM, OUT_DIM, REPS, preact_trainable=cfg["preact_trainable"],
+                                          base=basew is not None), dev)
     gx = torch.empty_like(t["x"])
     outs = dict(bucket.views, x=gx)
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)  # > 126 MB L2
 
     def step():
-        y = F.layer_forward(t["x"], t["theta"], t["pw"], t["pb"], t["postw"], t["postb"], None, None, **cfg)
-        F.layer_backward(t["x"], t["theta"], t["pw"], t["pb"], t["postw"], t["postb"], None, None,
-                         t["gy"], out=outs, **cfg)
+        y = F.layer_forward(t["x"], t["theta"], t["pw"], t["pb"], t["postw"], t["postb"], basew, None, **cfg)
+        F.layer_backward(t["x"], t["theta"], t["pw"], t["pb"], t["postw"], t["postb"], basew, None,
+                         t["gy"], out=outs, want=tuple(outs), **cfg)
         if world > 1:
             bucket.all_reduce()
         return y
@@ -259,11 +278,11 @@ def run_b200(args):
             flush.zero_()
             ev[k][0].record()
             fwd_ev[k][0].record()
-            F.layer_forward(t["x"], t["theta"], t["pw"], t["pb"], t["postw"], t["postb"], None, None, **cfg)
+            F.layer_forward(t["x"], t["theta"], t["pw"], t["pb"], t["postw"], t["postb"], basew, None, **cfg)
             fwd_ev[k][1].record()
             bwd_ev[k][0].record()
-            F.layer_backward(t["x"], t["theta"], t["pw"], t["pb"], t["postw"], t["postb"], None, None,
-                             t["gy"], out=outs, **cfg)
+            F.layer_backward(t["x"], t["theta"], t["pw"], t["pb"], t["postw"], t["postb"], basew, None,
+                             t["gy"], out=outs, want=tuple(outs), **cfg)
             bwd_ev[k][1].record()
             if world > 1:
                 bucket.all_reduce()
@@ -324,18 +343,19 @@ def run_b200(args):
     if rank == 0:
         peaks, peak_kind = measured_peaks()
         clk = clocks.summary()
-        wf, wm = work_per_edge(REPS)["fwd_bwd"]
+        work = work_per_edge(REPS, frozen=variant == "frozen")
+        wf, wm = work["fwd_bwd"]
         # step-level issue roofline (fwd + bwd), and the dominant kernel (the fused backward) alone
         lane_ops = edges_per_rank * (wf + wm)
         achieved = lane_ops / (fwd_ms + bwd_ms) * 1e-9  # Tlane-op/s on this rank
         peak_issue = SM_COUNT * FP32_LANES * NOMINAL_GHZ * 1e-3  # 37.23 Tlane-op/s
-        wfb, wmb = wf - work_per_edge(REPS)["fwd"][0], wm - work_per_edge(REPS)["fwd"][1]
+        wfb, wmb = wf - work["fwd"][0], wm - work["fwd"][1]
         bwd_achieved = edges_per_rank * (wfb + wmb) / bwd_ms * 1e-9
         alg_bytes = 4 * (2 * rows * IN_DIM + 2 * rows * OUT_DIM + rows * IN_DIM) + 3 * bucket.nbytes()
         roofline = {
             "bound": "fp32_issue", "achieved": achieved, "peak": peak_issue, "unit": "Tlane-op/s",
             "frac": achieved / peak_issue,
-            "roofline_ms": 1e3 * issue_roofline_seconds(edges_per_rank, REPS, "fwd_bwd"),
+            "roofline_ms": 1e3 * issue_roofline_seconds(edges_per_rank, REPS, "fwd_bwd", frozen=variant == "frozen"),
             "frac_at_sampled_clock": (achieved / (peak_issue * clk["sm_mhz"] / 1965.0)
                                       if clk.get("sm_mhz") else None),
             "peak_source": "148 SMs x 128 FP32 lanes x 1.965 GHz (issue roofline; SFU 16 lanes/SM)",
@@ -349,8 +369,10 @@ def run_b200(args):
                     "peak_gbs": peaks["hbm_gbs"], "peak_kind": peak_kind},
             "traffic": None,
         }
-        if rows == B_PER_GPU:
+        if rows == B_PER_GPU and variant == "headline":
             roofline["traffic"] = BACKWARD_DRAM_BYTES_PER_LAUNCH
+        if variant in ("base", "born"):
+            roofline["note"] = "work per edge is the headline's pinned count; this variant has no pinned count of its own"
         cpu = None
         if world == 1 and not args.no_cpu_baseline:
             cpu, _ = cpu_baseline(args.cpu_rows)
@@ -358,7 +380,8 @@ def run_b200(args):
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": args.scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": WORKLOAD if args.batch == B_PER_GPU else f"profiling-size run, batch {args.batch}",
+            "config": {"workload": (WORKLOAD if args.batch == B_PER_GPU else f"profiling-size run, batch {args.batch}")
+                       + ("" if variant == "headline" else f" [variant: {VARIANTS[variant]}]"),
                        "batch_per_gpu": rows, "global_batch": rows * world,
                        "in_dim": IN_DIM, "out_dim": OUT_DIM, "reps": REPS,
                        "parallelism": f"dp{world}", "l2": "flushed between timed steps (256 MB write)",
@@ -367,7 +390,7 @@ def run_b200(args):
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
             "gradient_exchange_ms": exchange_ms if world > 1 else 0.0,
-            "gpu_launches": 7 * args.steps,
+            "gpu_launches": (7 + (1 if basew is not None else 0)) * args.steps,
             "clocks": clk,
             "wall_s_timed_region": wall,
         }
@@ -390,6 +413,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     ap.add_argument("--e2e-chunks", type=int, default=4, help="row chunks of the host-buffer pipeline")
+    ap.add_argument("--variant", choices=tuple(VARIANTS), default="headline",
+                    help="extra rows of the microbenchmark; only the default is the benchmark line")
     ap.add_argument("--batch", type=int, default=B_PER_GPU,
                     help="rows per GPU; anything but the default is a profiling-size run, not the benchmark")
     args = ap.parse_args()

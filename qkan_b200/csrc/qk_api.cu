@@ -59,6 +59,8 @@ struct Layout {
     size_t table_off, bias_off, colsum_off, partials_off, total;
     size_t gtheta_off, gpw_off, gpb_off;  // per-edge gradients ahead of the group reduction (group > 0)
     size_t gxpart_off;                    // grad_x shares of the output slices (BwdCfg::osplit > 1)
+    size_t basepart_off;                  // row-tile partials of grad_base_weight (base-term kernel)
+    int base_tiles;
     int ncolsplit;
 };
 
@@ -77,15 +79,19 @@ Layout forward_layout(const QkDesc& d) {
     return l;
 }
 
-Layout backward_layout(const QkDesc& d, bool base) {
+Layout backward_layout(const QkDesc& d) {
     Layout l = forward_layout(d);
-    qk::BwdCfg c = qk::choose_bwd_cfg(d, base);
+    qk::BwdCfg c = qk::choose_bwd_cfg(d);
     l.ncolsplit = d.batch <= 0 ? 1 : (d.batch + 255) / 256;
     if (l.ncolsplit > 64) l.ncolsplit = 64;
     l.colsum_off = l.total;
     l.partials_off = l.colsum_off + qk::align256((size_t)l.ncolsplit * d.out_dim * sizeof(float));
     l.total = l.partials_off +
               qk::align256((size_t)c.grid_b * d.out_dim * c.nacc * l.ipad * sizeof(float));
+    const int base_tb = qk::base_rows_per_cta(d.batch, d.in_dim);
+    l.base_tiles = (d.batch + base_tb - 1) / base_tb;
+    l.basepart_off = l.total;
+    l.total += qk::align256((size_t)l.base_tiles * d.out_dim * l.ipad * sizeof(float));
     if (c.osplit > 1) {
         l.gxpart_off = l.total;
         l.total += qk::align256((size_t)c.osplit * d.batch * d.in_dim * sizeof(float));
@@ -206,7 +212,7 @@ int run_backward(const QkDesc* desc, const void* x, const float* theta, const fl
     if (!x || !theta || !pw || !pb) return fail(QK_ERR_BAD_ARGUMENT, "x/theta/preacts pointer is NULL");
     if (!edges && (!postw || !gy)) return fail(QK_ERR_BAD_ARGUMENT, "postact_weights or grad_y is NULL");
     const bool has_base = !edges && basew != nullptr;
-    Layout l = backward_layout(d, has_base);
+    Layout l = backward_layout(d);
     if (!ws || ws_bytes < l.total)
         return fail(QK_ERR_WORKSPACE, "workspace too small: need %zu bytes, got %zu", l.total, ws_bytes);
     if ((uintptr_t)ws % 256)
@@ -250,7 +256,7 @@ int run_backward(const QkDesc* desc, const void* x, const float* theta, const fl
     b.out_dim = d.out_dim;
     b.ipad = l.ipad;
     b.precise = (d.flags & QK_PRECISE_MATH) != 0;
-    b.cfg = qk::choose_bwd_cfg(d, has_base);
+    b.cfg = qk::choose_bwd_cfg(d);
     if (getenv("QK_DEBUG"))
         fprintf(stderr, "[qk] backward B=%d I=%d O=%d R=%d: %d groups x %d rows, grid %d x %d x %d output slices of %d, smem %zu, ru %d\n",
                 d.batch, d.in_dim, d.out_dim, d.reps, b.cfg.groups, b.cfg.rpg, b.cfg.grid_b, b.cfg.grid_i,
@@ -262,11 +268,30 @@ int run_backward(const QkDesc* desc, const void* x, const float* theta, const fl
     b.gx = gx;
     b.gx_part = b.cfg.osplit > 1 ? reinterpret_cast<float*>(wsb + l.gxpart_off) : nullptr;
     b.partials = reinterpret_cast<float*>(wsb + l.partials_off);
-    e = qk::launch_backward(b, p.rk, (d.flags & QK_FAST_MEASURE) != 0, d.io_dtype, has_base, st);
+    e = qk::launch_backward(b, p.rk, (d.flags & QK_FAST_MEASURE) != 0, d.io_dtype, st);
     if (e != cudaSuccess) return cuda_fail(e, "backward launch");
     if (gx && b.cfg.osplit > 1) {
         e = qk::launch_sum_gx(b.gx_part, gx, d.io_dtype, (size_t)d.batch * d.in_dim, b.cfg.osplit, st);
         if (e != cudaSuccess) return cuda_fail(e, "grad_x slice sum launch");
+    }
+    // base term: its two contractions run as a kernel of their own and add their part of grad_x in place
+    float* base_partials = reinterpret_cast<float*>(wsb + l.basepart_off);
+    const bool base_pass = has_base && (gx || gbasew);
+    if (base_pass) {
+        qk::BaseBwdArgs ba{};
+        ba.batch = d.batch;
+        ba.in_dim = d.in_dim;
+        ba.out_dim = d.out_dim;
+        ba.ipad = l.ipad;
+        ba.ks = qk::table_stride(p.rk);
+        ba.bw_row = qk::t_bw(p.rk);
+        ba.x = x;
+        ba.gy = gy;
+        ba.table = p.table;
+        ba.gx = gx;
+        ba.partials = gbasew ? base_partials : nullptr;
+        e = qk::launch_base_backward(ba, d.io_dtype, st);
+        if (e != cudaSuccess) return cuda_fail(e, "base-term backward launch");
     }
 
     if (gtheta || gpw || gpb || gpostw || gpostb || gbasew) {
@@ -280,7 +305,8 @@ int run_backward(const QkDesc* desc, const void* x, const float* theta, const fl
         f.nacc = b.cfg.nacc;
         f.ntiles = b.cfg.grid_b;
         f.ncolsplit = l.ncolsplit;
-        f.has_base = has_base;
+        f.base_tiles = has_base && gbasew ? l.base_tiles : 0;
+        f.base_partials = f.base_tiles ? base_partials : nullptr;
         f.flags = d.flags;
         f.param_dtype = d.param_dtype;
         f.partials = b.partials;
@@ -328,10 +354,7 @@ size_t qk_forward_workspace_bytes(const QkDesc* desc) {
 size_t qk_backward_workspace_bytes(const QkDesc* desc) {
     if (check_desc(desc)) return 0;
     if (empty(*desc)) return 256;
-    // sized for the larger of the two accumulator sets so one query covers both modes
-    return backward_layout(*desc, true).total > backward_layout(*desc, false).total
-               ? backward_layout(*desc, true).total
-               : backward_layout(*desc, false).total;
+    return backward_layout(*desc).total;
 }
 
 int qk_pz_forward(const QkDesc* desc, const void* x, const float* theta, const float* pw,

@@ -14,6 +14,8 @@
 // the groups' accumulators are summed through shared memory (block-level
 // reduction) and written as this batch tile's partial; finish_grads then sums
 // the tiles in a fixed order (cross-CTA reduction, bitwise reproducible).
+// The base term silu(x) @ base_weight has its own kernel (qk_base.cu): it is two small GEMMs, and carrying
+// silu(x) and silu'(x) through this kernel's shared-memory tile cost it a resident CTA.
 #pragma once
 #include <type_traits>
 
@@ -21,12 +23,10 @@
 
 namespace qk {
 
-__device__ __forceinline__ float sigmoid_f(float v) { return 1.f / (1.f + expf(-v)); }
-
 // Returns gx0 + d/dx of this edge (gx0 is the grad_x accumulated over the outputs walked so far).
-template <int R, bool FAST, bool BASE, bool EDGES, int NACC, bool PRECISE>
-__device__ __forceinline__ float edge_backward(const EdgeFwd<R>& e, float bw, float x, float g,
-                                               float sl, float dsl, float gx0, float (&acc)[NACC]) {
+template <int R, bool FAST, bool EDGES, int NACC, bool PRECISE>
+__device__ __forceinline__ float edge_backward(const EdgeFwd<R>& e, float x, float g, float gx0,
+                                               float (&acc)[NACC]) {
     if constexpr (R == 0) {
         // "real" ansatz: p = f(alpha), alpha = A x + C. acc[0] = sum dL/dalpha, acc[1] = sum dL/dalpha * x
         float s, c, r = 1.f;
@@ -42,12 +42,7 @@ __device__ __forceinline__ float edge_backward(const EdgeFwd<R>& e, float bw, fl
         const float ga = gp * dp;
         acc[0] += ga;
         acc[1] = fmaf(ga, x, acc[1]);
-        float gx = fmaf(ga, e.a, gx0);
-        if (BASE) {
-            acc[a_bw(0)] = fmaf(g, sl, acc[a_bw(0)]);
-            gx = fmaf(g * bw, dsl, gx);
-        }
-        return gx;
+        return fmaf(ga, e.a, gx0);
     } else {
     float cs[R], sn[R], vx, vy, vz, inv_rho, r;
     const float p = edge_forward<R, FAST, true, PRECISE>(e, x, cs, sn, vx, vy, vz, inv_rho, r);
@@ -90,21 +85,17 @@ __device__ __forceinline__ float edge_backward(const EdgeFwd<R>& e, float bw, fl
         }
     }
     acc[a_t00(R)] += wz;  // Rz(theta[0,0])
-    if (BASE) {
-        acc[a_bw(R)] = fmaf(g, sl, acc[a_bw(R)]);
-        gx = fmaf(g * bw, dsl, gx);
-    }
     return gx;
     }
 }
 
 constexpr int kGyChunk = 8;  // outputs whose grad_y columns are staged together
 
-template <int R, bool FAST, typename IO, bool BASE, bool EDGES, int RU, bool PRECISE, bool OSLICE>
+template <int R, bool FAST, typename IO, bool EDGES, int RU, bool PRECISE, bool OSLICE>
 __global__ void __launch_bounds__(256) backward_kernel(BwdArgs a) {
-    constexpr int NACC = acc_rows(R, BASE);
-    // floats per tile row: 32 (x, grad_x) pairs [+ 32 (silu, silu') pairs]; a pair is one 64-bit access
-    constexpr int ROW = BASE ? 128 : 64;
+    constexpr int NACC = acc_rows(R);
+    // floats per tile row: 32 (x, grad_x) pairs; a pair is one 64-bit access
+    constexpr int ROW = 64;
     extern __shared__ __align__(16) float smem[];
     const int groups = a.cfg.groups, rpg = a.cfg.rpg, tb = a.cfg.tb;
     float* xg_s = smem;                                  // [tb][ROW]
@@ -126,10 +117,6 @@ __global__ void __launch_bounds__(256) backward_kernel(BwdArgs a) {
         float v = 0.f;
         if (b0 + row < a.batch && i < a.in_dim) v = ld_as_float(x + (size_t)(b0 + row) * a.in_dim + i);
         *reinterpret_cast<float2*>(my + j * ROW) = make_float2(v, 0.f);
-        if (BASE) {
-            float sg = sigmoid_f(v);
-            *reinterpret_cast<float2*>(my + j * ROW + 64) = make_float2(v * sg, sg * (1.f + v * (1.f - sg)));
-        }
     }
     // a thread only ever touches its own column of its own group's rows: no barrier needed for xg_s
 
@@ -173,7 +160,6 @@ __global__ void __launch_bounds__(256) backward_kernel(BwdArgs a) {
             const int o = oc + ol;
             EdgeFwd<R> e;
             e.load(a.table + ((size_t)o * a.ipad + i) * KS);
-            const float bw = e.bw;
             float acc[NACC];
 #pragma unroll
             for (int k = 0; k < NACC; ++k) acc[k] = 0.f;
@@ -182,18 +168,12 @@ __global__ void __launch_bounds__(256) backward_kernel(BwdArgs a) {
             float* p = my;
 #pragma unroll 1
             for (int j = 0; j < rpg; j += RU, p += RU * ROW) {
-                float xv[RU], gxo[RU], g[RU], sl[RU], dsl[RU];
+                float xv[RU], gxo[RU], g[RU];
 #pragma unroll
                 for (int u = 0; u < RU; ++u) {
                     const float2 xg = *reinterpret_cast<const float2*>(p + u * ROW);
                     xv[u] = xg.x;
                     gxo[u] = xg.y;
-                    sl[u] = dsl[u] = 0.f;
-                    if (BASE) {
-                        const float2 sd = *reinterpret_cast<const float2*>(p + u * ROW + 64);
-                        sl[u] = sd.x;
-                        dsl[u] = sd.y;
-                    }
                     if (EDGES) {
                         const int b = b0 + row0 + j + u;
                         g[u] = 0.f;
@@ -219,8 +199,7 @@ __global__ void __launch_bounds__(256) backward_kernel(BwdArgs a) {
                 }
 #pragma unroll
                 for (int u = 0; u < RU; ++u) {
-                    p[u * ROW + 1] = edge_backward<R, FAST, BASE, EDGES, NACC, PRECISE>(e, bw, xv[u], g[u], sl[u],
-                                                                                     dsl[u], gxo[u], acc);
+                    p[u * ROW + 1] = edge_backward<R, FAST, EDGES, NACC, PRECISE>(e, xv[u], g[u], gxo[u], acc);
                 }
             }
 
@@ -257,19 +236,19 @@ __global__ void __launch_bounds__(256) backward_kernel(BwdArgs a) {
     }
 }
 
-template <int R, bool FAST, typename IO, bool BASE, bool EDGES>
+template <int R, bool FAST, typename IO, bool EDGES>
 static cudaError_t launch_bwd_t(const BwdArgs& a, cudaStream_t st) {
-    auto kern = a.cfg.ru == 4 ? backward_kernel<R, FAST, IO, BASE, EDGES, 4, false, false>
-                              : backward_kernel<R, FAST, IO, BASE, EDGES, 2, false, false>;
+    auto kern = a.cfg.ru == 4 ? backward_kernel<R, FAST, IO, EDGES, 4, false, false>
+                              : backward_kernel<R, FAST, IO, EDGES, 2, false, false>;
     if constexpr (std::is_same<IO, float>::value) {  // the full-precision variant exists for float32 I/O
-        if (a.precise) kern = backward_kernel<R, FAST, IO, BASE, EDGES, 2, true, false>;
+        if (a.precise) kern = backward_kernel<R, FAST, IO, EDGES, 2, true, false>;
     }
     if (a.cfg.osplit > 1) {
         // sliced outputs: one row-interleave per repetition count (rows per group are multiples of 4)
         constexpr int RU_S = (R > 8) ? 2 : 4;
-        kern = backward_kernel<R, FAST, IO, BASE, EDGES, RU_S, false, true>;
+        kern = backward_kernel<R, FAST, IO, EDGES, RU_S, false, true>;
         if constexpr (std::is_same<IO, float>::value) {
-            if (a.precise) kern = backward_kernel<R, FAST, IO, BASE, EDGES, 2, true, true>;
+            if (a.precise) kern = backward_kernel<R, FAST, IO, EDGES, 2, true, true>;
         }
     }
     cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -281,21 +260,17 @@ static cudaError_t launch_bwd_t(const BwdArgs& a, cudaStream_t st) {
 }
 
 template <int R, bool FAST, typename IO>
-static cudaError_t launch_bwd_r(const BwdArgs& a, bool has_base, cudaStream_t st) {
-    if (a.gpostacts) return launch_bwd_t<R, FAST, IO, false, true>(a, st);
-    if (has_base) return launch_bwd_t<R, FAST, IO, true, false>(a, st);
-    return launch_bwd_t<R, FAST, IO, false, false>(a, st);
+static cudaError_t launch_bwd_r(const BwdArgs& a, cudaStream_t st) {
+    if (a.gpostacts) return launch_bwd_t<R, FAST, IO, true>(a, st);
+    return launch_bwd_t<R, FAST, IO, false>(a, st);
 }
 
 template <int R>
-cudaError_t launch_bwd_d(const BwdArgs& a, bool fast, int io_dtype, bool has_base,
-                                cudaStream_t st) {
+cudaError_t launch_bwd_d(const BwdArgs& a, bool fast, int io_dtype, cudaStream_t st) {
     if (io_dtype == QK_BF16) {
-        return fast ? launch_bwd_r<R, true, __nv_bfloat16>(a, has_base, st)
-                    : launch_bwd_r<R, false, __nv_bfloat16>(a, has_base, st);
+        return fast ? launch_bwd_r<R, true, __nv_bfloat16>(a, st) : launch_bwd_r<R, false, __nv_bfloat16>(a, st);
     }
-    return fast ? launch_bwd_r<R, true, float>(a, has_base, st)
-                : launch_bwd_r<R, false, float>(a, has_base, st);
+    return fast ? launch_bwd_r<R, true, float>(a, st) : launch_bwd_r<R, false, float>(a, st);
 }
 
 }  // namespace qk

@@ -7,5 +7,5 @@
 #endif
 
 namespace qk {
-template cudaError_t launch_bwd_d<QK_INST_R>(const BwdArgs&, bool, int, bool, cudaStream_t);
+template cudaError_t launch_bwd_d<QK_INST_R>(const BwdArgs&, bool, int, cudaStream_t);
 }  // namespace qk

@@ -1,0 +1,140 @@
+// Backward of the base term  y += silu(x) @ (base_weight * mask)^T  of the layer epilogue
+// (reference: src/qkan/qkan.py:755, 784; the reference's fused epilogue leaves these two products to a
+// library GEMM, src/qkan/qkan_epilogue.py:517-522):
+//   grad_base_weight[o,i] = mask[o,i] * sum_b grad_y[b,o] * silu(x[b,i])
+//   grad_x[b,i]          += silu'(x[b,i]) * sum_o grad_y[b,o] * base_weight[o,i] * mask[o,i]
+// Both are (B x O x I) contractions with 2 FMAs per edge and row. They run here, after the circuit backward,
+// with the same mapping (lane = input column, CTA = rows x 32 columns, all outputs walked): silu(x) of the
+// thread's rows and the running sums for grad_x stay in registers, grad_y is staged transposed eight outputs
+// at a time and read back as 128-bit broadcasts, and the batch sum of grad_base_weight is reduced over the
+// warps in shared memory and written as one partial per (row tile, output) for finish_grads.
+#include "qk_kernels.cuh"
+
+namespace qk {
+
+namespace {
+
+constexpr int kBaseWarps = 8;
+constexpr int kBaseChunk = 8;  // outputs per staged grad_y chunk; equal to the warp count (one output per warp below)
+
+__device__ __forceinline__ float sigmoid_f(float v) { return 1.f / (1.f + expf(-v)); }
+
+template <typename IO, int RPW>
+__global__ void __launch_bounds__(kBaseWarps * kWarp, 3) base_backward_kernel(BaseBwdArgs a) {
+    constexpr int TB = kBaseWarps * RPW;  // rows per CTA
+    constexpr int LD = TB + 4;            // staged row length: keeps 128-bit alignment, spreads the banks
+    __shared__ __align__(16) float gy_s[2][kBaseChunk][LD];
+    __shared__ float bw_s[2][kBaseChunk][kWarp];
+    __shared__ float red_s[kBaseWarps][kBaseChunk][kWarp];
+    const int lane = threadIdx.x % kWarp, w = threadIdx.x / kWarp;
+    const int bt = blockIdx.x, b0 = bt * TB, row0 = w * RPW;
+    const int i = blockIdx.y * kWarp + lane;
+    const bool col_ok = i < a.in_dim;
+    const IO* __restrict__ x = static_cast<const IO*>(a.x);
+    const IO* __restrict__ gy = static_cast<const IO*>(a.gy);
+
+    float sl[RPW], gxb[RPW];
+#pragma unroll
+    for (int r = 0; r < RPW; ++r) {
+        const int b = b0 + row0 + r;
+        const float v = (b < a.batch && col_ok) ? ld_as_float(x + (size_t)b * a.in_dim + i) : 0.f;
+        sl[r] = v * sigmoid_f(v);
+        gxb[r] = 0.f;
+    }
+
+    // Software pipeline over chunks of 8 outputs: the next chunk's grad_y tile and base weights are fetched
+    // into registers while the current chunk is being multiplied, then stored to the other shared buffer.
+    constexpr int PER_THREAD = TB * kBaseChunk / (kBaseWarps * kWarp);  // staged grad_y values per thread
+    float gy_next[PER_THREAD], bw_next;
+    auto fetch = [&](int oc) {
+        const int nch = min(kBaseChunk, a.out_dim - oc);
+#pragma unroll
+        for (int q = 0; q < PER_THREAD; ++q) {
+            const int idx = threadIdx.x + q * (kBaseWarps * kWarp);
+            const int r = idx / kBaseChunk, c = idx % kBaseChunk;
+            gy_next[q] = (b0 + r < a.batch && c < nch) ? ld_as_float(gy + (size_t)(b0 + r) * a.out_dim + oc + c) : 0.f;
+        }
+        // thread (w, lane) fetches the weight of output oc + w for column i (one output per warp)
+        bw_next = (w < nch && col_ok) ? a.table[((size_t)(oc + w) * a.ipad + i) * a.ks + a.bw_row] : 0.f;
+    };
+    fetch(0);
+    int buf = 0;
+    for (int oc = 0; oc < a.out_dim; oc += kBaseChunk, buf ^= 1) {
+        const int nch = min(kBaseChunk, a.out_dim - oc);
+#pragma unroll
+        for (int q = 0; q < PER_THREAD; ++q) {
+            const int idx = threadIdx.x + q * (kBaseWarps * kWarp);
+            gy_s[buf][idx % kBaseChunk][idx / kBaseChunk] = gy_next[q];
+        }
+        bw_s[buf][w][lane] = bw_next;
+        __syncthreads();
+        if (oc + kBaseChunk < a.out_dim) fetch(oc + kBaseChunk);
+#pragma unroll 2
+        for (int c = 0; c < kBaseChunk; ++c) {
+            const float bw = bw_s[buf][c][lane];
+            float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;  // four independent chains for the batch sum
+#pragma unroll
+            for (int r = 0; r < RPW; r += 4) {
+                const float4 g = *reinterpret_cast<const float4*>(&gy_s[buf][c][row0 + r]);
+                gxb[r] = fmaf(g.x, bw, gxb[r]);
+                gxb[r + 1] = fmaf(g.y, bw, gxb[r + 1]);
+                gxb[r + 2] = fmaf(g.z, bw, gxb[r + 2]);
+                gxb[r + 3] = fmaf(g.w, bw, gxb[r + 3]);
+                s0 = fmaf(g.x, sl[r], s0);
+                s1 = fmaf(g.y, sl[r + 1], s1);
+                s2 = fmaf(g.z, sl[r + 2], s2);
+                s3 = fmaf(g.w, sl[r + 3], s3);
+            }
+            // written after this chunk's staging barrier, i.e. after the last chunk's reads
+            red_s[w][c][lane] = (s0 + s1) + (s2 + s3);
+        }
+        __syncthreads();
+        // warp w adds output oc + w over the warps (fixed order): this row tile's partial of grad_base_weight
+        if (a.partials && w < nch) {
+            float s = 0.f;
+#pragma unroll
+            for (int ww = 0; ww < kBaseWarps; ++ww) s += red_s[ww][w][lane];
+            a.partials[((size_t)bt * a.out_dim + oc + w) * a.ipad + i] = s;
+        }
+    }
+
+    if (a.gx && col_ok) {
+        IO* __restrict__ gx = static_cast<IO*>(a.gx);
+#pragma unroll
+        for (int r = 0; r < RPW; ++r) {
+            const int b = b0 + row0 + r;
+            if (b < a.batch) {
+                const size_t at = (size_t)b * a.in_dim + i;
+                const float v = ld_as_float(x + at);
+                const float sg = sigmoid_f(v);
+                const float dsl = sg * (1.f + v * (1.f - sg));
+                st_from_float(gx + at, fmaf(dsl, gxb[r], ld_as_float(gx + at)));
+            }
+        }
+    }
+}
+
+}  // namespace
+
+int base_rows_per_cta(int batch, int in_dim) {
+    // 128-row tiles (16 rows per warp, three CTAs resident per SM) unless that leaves SMs without work
+    // (small batches): then 64-row tiles
+    const long big = (long)((batch + 127) / 128) * ((in_dim + kWarp - 1) / kWarp);
+    return big >= 3 * 148 ? 128 : 64;
+}
+
+cudaError_t launch_base_backward(const BaseBwdArgs& a, int io_dtype, cudaStream_t st) {
+    const int tb = base_rows_per_cta(a.batch, a.in_dim);
+    dim3 grid((a.batch + tb - 1) / tb, a.ipad / kWarp);
+    const int threads = kBaseWarps * kWarp;
+    if (io_dtype == QK_BF16) {
+        if (tb == 128) base_backward_kernel<__nv_bfloat16, 16><<<grid, threads, 0, st>>>(a);
+        else base_backward_kernel<__nv_bfloat16, 8><<<grid, threads, 0, st>>>(a);
+    } else {
+        if (tb == 128) base_backward_kernel<float, 16><<<grid, threads, 0, st>>>(a);
+        else base_backward_kernel<float, 8><<<grid, threads, 0, st>>>(a);
+    }
+    return cudaPeekAtLastError();
+}
+
+}  // namespace qk

@@ -71,8 +71,7 @@ __host__ __device__ constexpr int a_c(int R, int l) { return R + 1 + l; }
 __host__ __device__ constexpr int a_pwx(int R, int l) { return 2 * R + 1 + l; }
 __host__ __device__ constexpr int a_t00(int R) { return 3 * R + 1; }
 __host__ __device__ constexpr int a_w(int R) { return 3 * R + 2; }
-__host__ __device__ constexpr int a_bw(int R) { return 3 * R + 3; }
-__host__ __device__ constexpr int acc_rows(int R, bool base) { return 3 * R + 3 + (base ? 1 : 0); }
+__host__ __device__ constexpr int acc_rows(int R) { return 3 * R + 3; }
 
 inline __host__ __device__ int round_up(int v, int m) { return (v + m - 1) / m * m; }
 inline __host__ __device__ size_t align256(size_t v) { return (v + 255) & ~size_t(255); }

@@ -18,11 +18,11 @@ static int tune_int(const char* name, int dflt) {
 template <int R>
 cudaError_t launch_fwd_d(const FwdArgs& a, bool fast, int io_dtype, bool has_base, cudaStream_t st);
 template <int R>
-cudaError_t launch_bwd_d(const BwdArgs& a, bool fast, int io_dtype, bool has_base, cudaStream_t st);
+cudaError_t launch_bwd_d(const BwdArgs& a, bool fast, int io_dtype, cudaStream_t st);
 
 #define QK_DECL(R)                                                                              \
     extern template cudaError_t launch_fwd_d<R>(const FwdArgs&, bool, int, bool, cudaStream_t); \
-    extern template cudaError_t launch_bwd_d<R>(const BwdArgs&, bool, int, bool, cudaStream_t);
+    extern template cudaError_t launch_bwd_d<R>(const BwdArgs&, bool, int, cudaStream_t);
 QK_DECL(0) QK_DECL(1) QK_DECL(2) QK_DECL(3) QK_DECL(4) QK_DECL(5) QK_DECL(6) QK_DECL(7) QK_DECL(8) QK_DECL(12) QK_DECL(16)
 #undef QK_DECL
 
@@ -65,14 +65,14 @@ FwdCfg choose_fwd_cfg(const QkDesc& d, bool edges, bool base, bool xtrig) {
     return best;
 }
 
-BwdCfg choose_bwd_cfg(const QkDesc& d, bool base) {
+BwdCfg choose_bwd_cfg(const QkDesc& d) {
     const int rk = compiled_reps(d.ansatz, d.reps);
-    const int nacc = acc_rows(rk, base);
+    const int nacc = acc_rows(rk);
     const int grid_i = (d.in_dim + 31) / 32;
     const int ru = tune_int("QK_BWD_RU", rk > 8 ? 2 : 4);  // long circuits: fewer rows in flight, no spills
     auto make = [&](int groups, int rpg) {
         const int tb = groups * rpg;
-        size_t smem = (size_t)tb * 32 * 4 * (base ? 4 : 2) + (size_t)kGyChunkHost * tb * 4 +
+        size_t smem = (size_t)tb * 32 * 4 * 2 + (size_t)kGyChunkHost * tb * 4 +
                       (size_t)2 * groups * nacc * 32 * 4;
         return BwdCfg{groups, rpg, tb, (d.batch + tb - 1) / tb, grid_i, nacc, smem, ru, 1, round_up(d.out_dim, kGyChunkHost)};
     };
@@ -180,20 +180,19 @@ cudaError_t launch_forward(const FwdArgs& a, int reps, bool fast, int io_dtype, 
     }
 }
 
-cudaError_t launch_backward(const BwdArgs& a, int reps, bool fast, int io_dtype, bool has_base,
-                            cudaStream_t st) {
+cudaError_t launch_backward(const BwdArgs& a, int reps, bool fast, int io_dtype, cudaStream_t st) {
     switch (reps) {
-        case 1: return launch_bwd_d<1>(a, fast, io_dtype, has_base, st);
-        case 2: return launch_bwd_d<2>(a, fast, io_dtype, has_base, st);
-        case 3: return launch_bwd_d<3>(a, fast, io_dtype, has_base, st);
-        case 4: return launch_bwd_d<4>(a, fast, io_dtype, has_base, st);
-        case 5: return launch_bwd_d<5>(a, fast, io_dtype, has_base, st);
-        case 6: return launch_bwd_d<6>(a, fast, io_dtype, has_base, st);
-        case 7: return launch_bwd_d<7>(a, fast, io_dtype, has_base, st);
-        case 8: return launch_bwd_d<8>(a, fast, io_dtype, has_base, st);
-        case 12: return launch_bwd_d<12>(a, fast, io_dtype, has_base, st);
-        case 16: return launch_bwd_d<16>(a, fast, io_dtype, has_base, st);
-        case 0: return launch_bwd_d<0>(a, fast, io_dtype, has_base, st);
+        case 1: return launch_bwd_d<1>(a, fast, io_dtype, st);
+        case 2: return launch_bwd_d<2>(a, fast, io_dtype, st);
+        case 3: return launch_bwd_d<3>(a, fast, io_dtype, st);
+        case 4: return launch_bwd_d<4>(a, fast, io_dtype, st);
+        case 5: return launch_bwd_d<5>(a, fast, io_dtype, st);
+        case 6: return launch_bwd_d<6>(a, fast, io_dtype, st);
+        case 7: return launch_bwd_d<7>(a, fast, io_dtype, st);
+        case 8: return launch_bwd_d<8>(a, fast, io_dtype, st);
+        case 12: return launch_bwd_d<12>(a, fast, io_dtype, st);
+        case 16: return launch_bwd_d<16>(a, fast, io_dtype, st);
+        case 0: return launch_bwd_d<0>(a, fast, io_dtype, st);
         default: return cudaErrorInvalidValue;
     }
 }

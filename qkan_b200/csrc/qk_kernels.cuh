@@ -25,7 +25,9 @@ struct PrepArgs {
 };
 
 struct FinishArgs {
-    int in_dim, out_dim, reps, ipad, nacc, ntiles, ncolsplit, has_base;
+    int in_dim, out_dim, reps, ipad, nacc, ntiles, ncolsplit;
+    int base_tiles;               // row tiles of the base-term kernel (0: no base term)
+    const float* base_partials;   // [base_tiles][out_dim][ipad] partial sums of grad_base_weight
     int rk, ansatz;
     unsigned flags;
     int param_dtype;
@@ -89,8 +91,21 @@ struct BwdArgs {
     float* partials;
 };
 
+// Backward of the base term (qk_base.cu): runs after the circuit backward, adds its part to grad_x in place.
+struct BaseBwdArgs {
+    int batch, in_dim, out_dim, ipad;
+    int ks, bw_row;      // stride of an edge's constants in the table and the row of base_weight * mask within it
+    const void* x;
+    const void* gy;
+    const float* table;
+    void* gx;            // read-modify-write; nullptr: grad_x not wanted
+    float* partials;     // [row tiles][out_dim][ipad]; nullptr: grad_base_weight not wanted
+};
+
 FwdCfg choose_fwd_cfg(const QkDesc& d, bool edges, bool base, bool xtrig);
-BwdCfg choose_bwd_cfg(const QkDesc& d, bool base);
+BwdCfg choose_bwd_cfg(const QkDesc& d);
+int base_rows_per_cta(int batch, int in_dim);
+cudaError_t launch_base_backward(const BaseBwdArgs& a, int io_dtype, cudaStream_t st);
 
 cudaError_t launch_prep(const PrepArgs& a, cudaStream_t st);
 cudaError_t launch_colsum(const void* gy, int io_dtype, int B, int O, int nsplit, float* part,
@@ -103,7 +118,6 @@ cudaError_t launch_group_reduce(const float* src, float* dst, int out_dim, int i
                                 cudaStream_t st);
 cudaError_t launch_forward(const FwdArgs& a, int reps, bool fast, int io_dtype, bool has_base,
                            cudaStream_t st);
-cudaError_t launch_backward(const BwdArgs& a, int reps, bool fast, int io_dtype, bool has_base,
-                            cudaStream_t st);
+cudaError_t launch_backward(const BwdArgs& a, int reps, bool fast, int io_dtype, cudaStream_t st);
 
 }  // namespace qk

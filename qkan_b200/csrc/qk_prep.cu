@@ -133,19 +133,27 @@ __global__ void colsum_kernel(const IO* __restrict__ gy, int B, int O, int nspli
 // partials t = slice, slice + slices, ... of each accumulator row; slice 0 then adds the slice sums in
 // order and writes the gradients. Fixed order throughout: run-to-run bitwise reproducible.
 __global__ void finish_grads_kernel(FinishArgs a) {
-    extern __shared__ float part[];  // [slices][nacc][32]
+    extern __shared__ float part[];  // [slices][nacc + 1][32]; the extra row is the base-term kernel's partials
     const int lane = threadIdx.x, slice = threadIdx.y, slices = blockDim.y;
     const int i = blockIdx.x * kWarp + lane;  // < ipad
     const int o = blockIdx.y;
     const int R = a.reps, RK = a.rk;
-    const int nacc = a.nacc;
+    const int nacc = a.nacc, nrow = a.nacc + 1;
     const size_t tile_stride = (size_t)a.out_dim * nacc * a.ipad;
     const float* p0 = a.partials + ((size_t)o * nacc) * a.ipad + i;
     for (int k = 0; k < nacc; ++k) {
         const float* p = p0 + (size_t)k * a.ipad;
         float s = 0.f;
         for (int t = slice; t < a.ntiles; t += slices) s += p[(size_t)t * tile_stride];
-        part[(slice * nacc + k) * kWarp + lane] = s;
+        part[(slice * nrow + k) * kWarp + lane] = s;
+    }
+    {
+        float s = 0.f;
+        if (a.base_partials) {
+            const float* bp = a.base_partials + (size_t)o * a.ipad + i;
+            for (int t = slice; t < a.base_tiles; t += slices) s += bp[(size_t)t * a.out_dim * a.ipad];
+        }
+        part[(slice * nrow + nacc) * kWarp + lane] = s;
     }
     __syncthreads();
     if (slice != 0 || i >= a.in_dim) return;
@@ -154,7 +162,7 @@ __global__ void finish_grads_kernel(FinishArgs a) {
     const bool use_pb = (a.flags & QK_USE_POSTACT_BIAS) != 0 && a.postb != nullptr;
     auto total = [&](int k) {
         float s = 0.f;
-        for (int w = 0; w < slices; ++w) s += part[(w * nacc + k) * kWarp + lane];
+        for (int w = 0; w < slices; ++w) s += part[(w * nrow + k) * kWarp + lane];
         return s;
     };
     if (a.ansatz == QK_ANSATZ_REAL) {
@@ -202,7 +210,7 @@ __global__ void finish_grads_kernel(FinishArgs a) {
             float w = a.postw ? ld_param(a.postw, a.param_dtype, e) * m : 1.f;
             a.gpostb[e] = use_pb ? w * cs : 0.f;
         }
-        if (a.gbasew) a.gbasew[e] = a.has_base ? m * total(a_bw(RK)) : 0.f;
+        if (a.gbasew) a.gbasew[e] = m * total(nacc);
     }
 }
 
@@ -273,10 +281,11 @@ cudaError_t launch_colsum(const void* gy, int io_dtype, int B, int O, int nsplit
 cudaError_t launch_finish(const FinishArgs& a, cudaStream_t st) {
     // as many tile slices as there are tiles to share out, within 48 KB of shared memory
     int slices = 8;
-    while (slices > 1 && (slices / 2 >= a.ntiles || (size_t)slices * a.nacc * kWarp * sizeof(float) > 48 * 1024))
+    const int most_tiles = a.ntiles > a.base_tiles ? a.ntiles : a.base_tiles;
+    while (slices > 1 && (slices / 2 >= most_tiles || (size_t)slices * (a.nacc + 1) * kWarp * sizeof(float) > 48 * 1024))
         slices /= 2;
     dim3 grid(a.ipad / kWarp, a.out_dim), block(kWarp, slices);
-    finish_grads_kernel<<<grid, block, (size_t)slices * a.nacc * kWarp * sizeof(float), st>>>(a);
+    finish_grads_kernel<<<grid, block, (size_t)slices * (a.nacc + 1) * kWarp * sizeof(float), st>>>(a);
     return cudaPeekAtLastError();
 }
 
