@@ -96,28 +96,43 @@ BwdCfg choose_bwd_cfg(const QkDesc& d) {
     double best_cost = -1.0;
     for (int pass = 0; pass < 2 && best_cost < 0; ++pass) {
         for (auto& c : cand) {
-            BwdCfg cur = make(c[0], c[1]);
-            if (cur.smem > 200 * 1024) continue;
-            const double partial_bytes = (double)cur.grid_b * d.out_dim * nacc * ipad * 4.0;
-            if (pass == 0 && partial_bytes > partial_cap) continue;  // second pass lifts the cap if nothing fits
-            const long ctas = (long)cur.grid_b * grid_i;
-            long resident = (long)(kSmemPerSm / (cur.smem + 1024));
-            const long by_regs = 65536 / ((long)regs_est * cur.groups * 32);
-            if (by_regs < resident) resident = by_regs;
-            if (resident < 1) resident = 1;
-            const long per_sm = (ctas + kSmCount - 1) / kSmCount;
-            const long live = per_sm < resident ? per_sm : resident;
-            const double warps = (double)live * cur.groups;
-            const double occupancy =
-                warps >= 16 ? 1.0 : (warps >= 8 ? 1.0 + 0.04 * (16 - warps) : 1.32 + 0.2 * (8 - warps));
-            const double setup = 1.0 + 0.09 * 32.0 / cur.rpg;       // per-edge set-up and reduction per row
-            const double small_cta = 1.0 + 0.02 * (8.0 / cur.groups - 1.0);
-            const double compute = (double)per_sm * cur.tb * d.out_dim * t_unit * setup * occupancy * small_cta;
-            const double partials = 2.0 * partial_bytes / 6.0e12;  // written here, read by finish_grads
-            const double cost = compute + partials;
-            if (best_cost < 0 || cost < best_cost * 0.999) {
-                best = cur;
-                best_cost = cost;
+            // output slices (grid.z) give the CTA count a finer grain: fewer partly filled waves; their price
+            // is one more pass over grad_x and a tile prologue per slice
+            for (int want = 1; want <= 8; want *= 2) {
+                if (want > 1 && (d.out_dim < 32 || force_osplit > 0)) break;
+                BwdCfg cur = slice(make(c[0], c[1]), want);
+                if (want > 1 && cur.osplit <= want / 2) continue;  // same slicing as a smaller `want`
+                if (cur.smem > 200 * 1024) continue;
+                const double partial_bytes = (double)cur.grid_b * d.out_dim * nacc * ipad * 4.0;
+                if (pass == 0 && partial_bytes > partial_cap) continue;  // second pass lifts the cap if nothing fits
+                const long ctas = (long)cur.grid_b * grid_i * cur.osplit;
+                long resident = (long)(kSmemPerSm / (cur.smem + 1024));
+                const long by_regs = 65536 / ((long)regs_est * cur.groups * 32);
+                if (by_regs < resident) resident = by_regs;
+                if (resident < 1) resident = 1;
+                const long per_sm = (ctas + kSmCount - 1) / kSmCount;
+                const long live = per_sm < resident ? per_sm : resident;
+                const double warps = (double)live * cur.groups;
+                const double occupancy =
+                    warps >= 16 ? 1.0 : (warps >= 8 ? 1.0 + 0.04 * (16 - warps) : 1.32 + 0.2 * (8 - warps));
+                const double setup = 1.0 + 0.09 * 32.0 / cur.rpg;       // per-edge set-up and reduction per row
+                const double small_cta = 1.0 + 0.02 * (8.0 / cur.groups - 1.0);
+                const int o_cta = cur.osplit > 1 ? cur.ochunk : d.out_dim;
+                // a partly filled last wave costs less than a full one (its CTAs have the SM's issue slots to
+                // themselves): count it half-way between its share and a whole wave
+                const double waves = 0.5 * ((double)ctas / kSmCount + (double)per_sm);
+                // measured: a sliced launch costs a few per cent more than its share of the work, more so for
+                // short circuits (8192 x 512 x 512, 1 repetition: +4 % where the wave count predicted -12 %)
+                const double slice_tax = cur.osplit > 1 ? 1.0 + 0.12 / (rk + 0.5) : 1.0;
+                const double compute = waves * cur.tb * o_cta * t_unit * setup * occupancy * small_cta * slice_tax;
+                const double partials = 2.0 * partial_bytes / 6.0e12;  // written here, read by finish_grads
+                const double sliced = cur.osplit > 1 ? 4.0e-6 + (double)(cur.osplit + 1) * d.batch * d.in_dim * 4.0 / 3.0e12
+                                                     : 0.0;
+                const double cost = compute + partials + sliced;
+                if (best_cost < 0 || cost < best_cost * 0.999) {
+                    best = cur;
+                    best_cost = cost;
+                }
             }
         }
     }
@@ -126,7 +141,7 @@ BwdCfg choose_bwd_cfg(const QkDesc& d) {
     // dependent chain of one output after the other (constant load, rows, reduction), not issue slots.
     // Smaller tiles and output slices put more chains in flight. Per output a warp spends about
     // 0.8 us + its rows x 0.175 us (measured at 3 repetitions, scaled by the instruction count).
-    if ((long)best.grid_b * grid_i * best.groups >= kSmCount * 16 || d.batch <= 0) return best;
+    if ((long)best.grid_b * grid_i * best.osplit * best.groups >= kSmCount * 16 || d.batch <= 0) return best;
     static const int small[][2] = {{8, 16}, {8, 8}, {4, 8}, {8, 4}, {4, 4}, {2, 8}, {2, 4}};
     const double chain0 = 0.8e-6, chain_row = 0.175e-6 * (28.0 * rk + 20.0) / 104.0;
     best_cost = -1.0;
