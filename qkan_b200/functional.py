@@ -250,9 +250,12 @@ class _LayerFunction(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, theta, pw, pb, postw, postb, basew, mask, preact_trainable, fast_measure,
                 use_postact_bias, ansatz, precise):
-        ctx.save_for_backward(x, theta, pw, pb, postw, postb, basew, mask)
+        # theta / preacts reach the kernels as float32; converted once here and kept for the backward
+        theta32, pw32, pb32 = _f32c(theta), _f32c(pw), _f32c(pb)
+        ctx.save_for_backward(x, theta32, pw32, pb32, postw, postb, basew, mask)
         ctx.cfg = (preact_trainable, fast_measure, use_postact_bias, ansatz, precise)
-        return layer_forward(x, theta, pw, pb, postw, postb, basew, mask,
+        ctx.meta = [(t.dtype, t.shape) if t is not None else None for t in (x, theta, pw, pb, postw, postb, basew)]
+        return layer_forward(x, theta32, pw32, pb32, postw, postb, basew, mask,
                              preact_trainable=preact_trainable, fast_measure=fast_measure,
                              use_postact_bias=use_postact_bias, ansatz=ansatz, precise=precise)
 
@@ -273,12 +276,12 @@ class _LayerFunction(torch.autograd.Function):
         g = layer_backward(x, theta, pw, pb, postw, postb, basew, mask, gy,
                            preact_trainable=preact_trainable, fast_measure=fast_measure,
                            use_postact_bias=use_postact_bias, want=want, ansatz=ansatz, precise=precise)
-        srcs = (x, theta, pw, pb, postw, postb, basew)
         outs = []
         for k, n in enumerate(names):
             t = g.get(n)
-            if t is not None and srcs[k] is not None:
-                t = t.to(srcs[k].dtype).reshape(srcs[k].shape)
+            if t is not None and ctx.meta[k] is not None:
+                dtype, shape = ctx.meta[k]
+                t = t.to(dtype).reshape(shape)
             outs.append(t)
         return (*outs, None, None, None, None, None, None)
 
