@@ -224,6 +224,10 @@ def run_b200(args):
             raise SystemExit("launch with torch.distributed.run --nproc-per-node N for --gpus N > 1")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    from qkan_b200.parallel import bind_host_thread_near_gpu
+
+    all_cores = os.sched_getaffinity(0)
+    numa_cores = bind_host_thread_near_gpu(local_rank)  # host buffers next to this rank's GPU
     if world > 1:
         # NCCL prints its version banner with printf when NCCL_DEBUG is set; stdout carries the one JSON line
         # only, so file descriptor 1 points at stderr while the communicator comes up
@@ -346,6 +350,7 @@ def run_b200(args):
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
         e2e_ms = float(tt.item())
     e2e_value = edges_per_rank * world * REPS / (e2e_ms * 1e-3)
+    os.sched_setaffinity(0, all_cores)  # the CPU baseline below gets every core again
     h2d = hx.numel() * 4 + hgy.numel() * 4
     d2h = hy.numel() * 4 + hgx.numel() * 4 + hgrads.numel() * 4
 
@@ -399,6 +404,7 @@ def run_b200(args):
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
             "gradient_exchange_ms": exchange_ms if world > 1 else 0.0,
+            "host_cores_near_gpu": numa_cores,
             "gpu_launches": (7 + (1 if basew is not None else 0)) * args.steps,
             "clocks": clk,
             "wall_s_timed_region": wall,

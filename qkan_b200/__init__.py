@@ -8,8 +8,8 @@ from .layer import QKANLayer, SOLVER_NAME
 from .model import QKAN
 from .hqkan import FusedHQKAN
 from .solver import B200Solver, get_registry, get_solver, register, register_with_reference
-from .parallel import GradBucket, get_dist_info, print0, shard_rows
+from .parallel import GradBucket, bind_host_thread_near_gpu, get_dist_info, print0, shard_rows
 
 __version__ = "0.1.0"
-__all__ = ["QKAN", "QKANLayer", "FusedHQKAN", "B200Solver", "GradBucket", "SOLVER_NAME", "get_dist_info",
+__all__ = ["QKAN", "QKANLayer", "FusedHQKAN", "B200Solver", "GradBucket", "SOLVER_NAME", "bind_host_thread_near_gpu", "get_dist_info",
            "get_registry", "get_solver", "print0", "register", "register_with_reference", "shard_rows"]

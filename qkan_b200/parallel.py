@@ -78,6 +78,35 @@ class GradBucket:
         return self.flat.numel() * self.flat.element_size()
 
 
+def bind_host_thread_near_gpu(device_index: int) -> Optional[int]:
+    """Pin the calling thread to the CPU cores NVML lists as local to this GPU (same NUMA node / PCIe root).
+
+    With one process per GPU, pinned host buffers allocated afterwards land in memory next to the GPU, so the
+    ranks' host<->device copies do not all cross the same inter-socket link. Touches only this process's CPU
+    affinity (no GPU setting). Returns the number of cores in the new mask, or None when NVML, the device or
+    the container's cpuset does not allow it (nothing is changed then).
+    """
+    try:
+        import pynvml
+
+        pynvml.nvmlInit()
+        uuid = str(torch.cuda.get_device_properties(device_index).uuid)
+        try:
+            handle = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + uuid).encode())
+        except Exception:
+            handle = pynvml.nvmlDeviceGetHandleByIndex(device_index)
+        n_words = (os.cpu_count() + 63) // 64
+        mask = pynvml.nvmlDeviceGetCpuAffinity(handle, n_words)
+        local = {64 * w + b for w, word in enumerate(mask) for b in range(64) if (int(word) >> b) & 1}
+        allowed = local & os.sched_getaffinity(0)
+        if not allowed:
+            return None
+        os.sched_setaffinity(0, allowed)
+        return len(allowed)
+    except Exception:
+        return None
+
+
 def layer_grad_shapes(in_dim: int, out_dim: int, reps: int, *, preact_trainable: bool = True,
                       postact_bias: bool = True, base: bool = False) -> Dict[str, Tuple[int, ...]]:
     """Shapes of the parameter gradients of one layer, in the order they are packed."""
