@@ -262,3 +262,43 @@ def test_backward_with_sliced_outputs_matches_oracle(monkeypatch, io_dtype, prec
     g1 = F.postacts_backward(x, th, pw, pb, gpa, preact_trainable=True, precise=precise)
     for k in g1:
         assert nerr(gs[k].cpu().numpy(), g1[k].cpu().numpy()) <= 2e-6, k
+
+
+def test_seeded_random_shapes_and_flags_vs_oracle():
+    """Forty seeded problems over shape, repetitions, ansatz, flags, grouping and dtype: every tile choice
+    the dispatcher can make at these sizes (row tiles, output slices, padded circuits) against the oracle."""
+    rng = np.random.default_rng(2024)
+    for case in range(40):
+        ansatz = ("pz", "pz", "rpz", "real")[case % 4]
+        B = int(rng.choice([1, 7, 33, 130, 513, 1100]))
+        I = int(rng.choice([1, 5, 32, 33, 70, 200]))
+        O = int(rng.choice([1, 3, 16, 40, 97, 160]))
+        R = int(rng.choice([1, 2, 3, 5, 9]))
+        if B * I * O > 6_000_000:
+            B = max(1, 6_000_000 // (I * O))
+        p = random_problem(1000 + case, B, I, O, R, use_pb=bool(case % 3), base=bool(case % 2), masked=bool(case % 5 == 0))
+        layers, width = {"pz": (R + 1, 2), "rpz": (R + 1, 1), "real": (R, 1)}[ansatz]
+        group = int(rng.choice([0, 0, 1, 3, 8]))
+        lead = (group,) if group else (O, I)
+        p["theta"] = rng.uniform(-np.pi, np.pi, lead + (layers, width)).astype(np.float32)
+        p["pw"] = (1 + 0.2 * rng.standard_normal(lead + (R,))).astype(np.float32)
+        p["pb"] = (0.2 * rng.standard_normal(lead + (R,))).astype(np.float32)
+        cfg = dict(preact_trainable=bool(case % 2 == 0), fast_measure=bool(case % 3 != 1),
+                   use_postact_bias=p["postb"] is not None, ansatz=ansatz)
+        y, g = _run_cuda(p, cfg, precise=bool(case % 7 == 0))
+        q = dict(p)
+        if group:
+            for k in ("theta", "pw", "pb"):
+                q[k] = expand_group(p[k], O, I)
+        y_ref, g_ref = _run_oracle(q, cfg)
+        if group:
+            for k in ("theta", "preacts_weight", "preacts_bias"):
+                g_ref[k] = reduce_group(g_ref[k], group)
+        label = f"case {case}: {ansatz} B{B} I{I} O{O} R{R} group {group} {cfg}"
+        assert nerr(y, y_ref) <= TOL_F32, label
+        for k in GRAD_NAMES:
+            if k == "base_weight" and p["basew"] is None:
+                continue
+            if k == "postact_bias" and p["postb"] is None:
+                continue
+            assert nerr(g[k], g_ref[k]) <= TOL_F32, f"{label}: grad {k} err {nerr(g[k], g_ref[k]):.3e}"
