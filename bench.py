@@ -427,7 +427,7 @@ def main():
     ap.add_argument("--ref-rows", type=int, default=256, help="rows per step of --impl reference")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
-    ap.add_argument("--e2e-chunks", type=int, default=4, help="row chunks of the host-buffer pipeline")
+    ap.add_argument("--e2e-chunks", type=int, default=3, help="row chunks of the host-buffer pipeline")
     ap.add_argument("--variant", choices=tuple(VARIANTS), default="headline",
                     help="extra rows of the microbenchmark; only the default is the benchmark line")
     ap.add_argument("--batch", type=int, default=B_PER_GPU,

@@ -120,8 +120,8 @@ def _preact_shape(desc: _abi.QkDesc):
 def layer_forward(x, theta, pw, pb, postw, postb=None, basew=None, mask=None, *,
                   preact_trainable: bool, fast_measure: bool = True,
                   use_postact_bias: bool = False, ansatz: str = "pz_encoding",
-                  precise: bool = False) -> torch.Tensor:
-    """``y (B,O)`` of the fused layer; no autograd (see ``qkan_layer``)."""
+                  precise: bool = False, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``y (B,O)`` of the fused layer; no autograd (see ``qkan_layer``). ``out``: preallocated contiguous result."""
     lib = _abi.load()
     _require_cuda(x, "x")
     x = x.detach().contiguous()
@@ -129,7 +129,13 @@ def layer_forward(x, theta, pw, pb, postw, postb=None, basew=None, mask=None, *,
     postw, postb, basew, mask, pdt = _oi_params(postw, postb if use_postact_bias else None, basew, mask)
     desc = _make_desc(x, theta, _flags(preact_trainable, fast_measure, use_postact_bias and postb is not None, precise), pdt, ansatz,
                       out_dim=postw.shape[0])
-    y = torch.empty((x.shape[0], desc.out_dim), dtype=x.dtype, device=x.device)
+    if out is None:
+        y = torch.empty((x.shape[0], desc.out_dim), dtype=x.dtype, device=x.device)
+    else:
+        y = out
+        if (tuple(y.shape) != (x.shape[0], desc.out_dim) or y.dtype != x.dtype or y.device != x.device
+                or not y.is_contiguous()):
+            raise ValueError(f"out must be a contiguous {x.dtype} tensor of {(x.shape[0], desc.out_dim)} on {x.device}")
     with torch.cuda.device(x.device):
         nbytes = lib.qk_forward_workspace_bytes(_abi.desc_pointer(desc))
         ws = _workspace(x.device, nbytes)

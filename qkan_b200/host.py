@@ -31,7 +31,7 @@ from .parallel import GradBucket, layer_grad_shapes
 class HostLayerPipeline:
     """Chunked, stream-overlapped ``y, grad_x, parameter gradients`` from host-resident ``x, grad_y``."""
 
-    def __init__(self, batch: int, in_dim: int, out_dim: int, reps: int, device, *, n_chunks: int = 4,
+    def __init__(self, batch: int, in_dim: int, out_dim: int, reps: int, device, *, n_chunks: int = 3,
                  dtype: torch.dtype = torch.float32, preact_trainable: bool = True,
                  fast_measure: bool = True, use_postact_bias: bool = True, ansatz: str = "pz_encoding",
                  row_align: int = 148 * 64):
@@ -41,12 +41,13 @@ class HostLayerPipeline:
         n_chunks = max(1, min(n_chunks, batch))
         step = (batch + n_chunks - 1) // n_chunks
         if row_align > 1 and batch >= 2 * row_align:  # whole waves per chunk; the last chunk takes the remainder
-            step = max(row_align, (step + row_align // 2) // row_align * row_align)
+            step = (step + row_align - 1) // row_align * row_align
         self.spans = [(b, min(batch, b + step)) for b in range(0, batch, step)]
         dev = self.device
         self.dx = [torch.empty((e - b, in_dim), dtype=dtype, device=dev) for b, e in self.spans]
         self.dgy = [torch.empty((e - b, out_dim), dtype=dtype, device=dev) for b, e in self.spans]
         self.dgx = [torch.empty((e - b, in_dim), dtype=dtype, device=dev) for b, e in self.spans]
+        self.dy = [torch.empty((e - b, out_dim), dtype=dtype, device=dev) for b, e in self.spans]
         shapes = layer_grad_shapes(in_dim, out_dim, reps, preact_trainable=preact_trainable,
                                    postact_bias=use_postact_bias)
         if ansatz in ("rpz_encoding", "rpz"):
@@ -81,9 +82,9 @@ class HostLayerPipeline:
                 self.ev_in[k].record(self.s_in)
             compute.wait_event(self.ev_in[k])
             if not self._first:
-                compute.wait_event(self.ev_free[k])  # the previous step's grad_x of this chunk has left the device
+                compute.wait_event(self.ev_free[k])  # the previous step's y and grad_x of this chunk have left the device
             y = qf.layer_forward(self.dx[k], p["theta"], p["pw"], p["pb"], p["postw"], p.get("postb"),
-                                 p.get("basew"), p.get("mask"), **self.cfg)
+                                 p.get("basew"), p.get("mask"), out=self.dy[k], **self.cfg)
             outs = dict(self.chunk_buckets[k].views, x=self.dgx[k])
             qf.layer_backward(self.dx[k], p["theta"], p["pw"], p["pb"], p["postw"], p.get("postb"),
                               p.get("basew"), p.get("mask"), self.dgy[k], out=outs,
@@ -94,7 +95,6 @@ class HostLayerPipeline:
                 hy[b:e].copy_(y, non_blocking=True)
                 hgx[b:e].copy_(self.dgx[k], non_blocking=True)
                 self.ev_free[k].record(self.s_out)
-            y.record_stream(self.s_out)
         flat = self.bucket.flat
         if not self._first:
             compute.wait_event(self.ev_sum_free)  # the previous step's gradients have left the device

@@ -157,7 +157,7 @@ def test_host_pipeline_matches_the_direct_call():
             assert nerr(bucket[name].cpu().numpy(), g_ref[name].cpu().numpy()) <= 2e-6, name
     # back-to-back steps without a synchronisation in between (copy-out of one step under the next step's
     # kernels), chunk boundaries on multiples of 256 rows, gradients copied to the host as well
-    pipe = HostLayerPipeline(B, I, O, R, "cuda:0", n_chunks=3, row_align=256)
+    pipe = HostLayerPipeline(B, I, O, R, "cuda:0", n_chunks=4, row_align=256)
     assert [e - b for b, e in pipe.spans] == [256, 256, 256, 232]
     hgrads = torch.empty(pipe.bucket.flat.numel()).pin_memory()
     hy.zero_(), hgx.zero_()
