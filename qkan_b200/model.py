@@ -280,7 +280,10 @@ class QKAN(nn.Module):
             optimizer.zero_grad()
             return objective_and_backward()
 
-        is_lbfgs = isinstance(optimizer, torch.optim.LBFGS)
+        # closure-driven optimisers: torch's LBFGS, and composites that hand the closure on to one (the
+        # reference's LBFGSFinisher, src/qkan/optim/lbfgs.py:46-130, or anything that sets `needs_closure`)
+        is_lbfgs = (isinstance(optimizer, torch.optim.LBFGS) or bool(getattr(optimizer, "needs_closure", False))
+                    or type(optimizer).__name__ == "LBFGSFinisher")
         if closure is None and is_lbfgs:
             closure = default_closure
 

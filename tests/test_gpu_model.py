@@ -286,3 +286,35 @@ def test_hybrid_block_bf16_eager_and_graphed(ansatz):
     for n, p in block.named_parameters():
         if n in eager:
             assert nerr(p.grad.float().cpu().numpy(), eager[n].float().cpu().numpy()) <= 1e-6, n
+
+
+def test_train_loop_with_a_closure_driven_composite_optimizer():
+    """An optimiser that runs Adam first and hands the closure to LBFGS later (the shape of the reference's
+    `adam_then_lbfgs`) goes through train_ like LBFGS itself: it gets the built-in closure."""
+
+    class AdamThenLbfgs:
+        needs_closure = True
+
+        def __init__(self, params, switch_at):
+            self.params, self.switch_at, self.calls = list(params), switch_at, 0
+            self.adam = torch.optim.Adam(self.params, lr=1e-2)
+            self.lbfgs = None
+
+        def zero_grad(self, set_to_none=True):
+            (self.lbfgs or self.adam).zero_grad(set_to_none=set_to_none)
+
+        def step(self, closure):
+            self.calls += 1
+            if self.calls > self.switch_at and self.lbfgs is None:
+                self.lbfgs = torch.optim.LBFGS(self.params, lr=0.5, max_iter=5, line_search_fn="strong_wolfe")
+            return (self.lbfgs or self.adam).step(closure)
+
+    torch.manual_seed(0)
+    x = torch.rand(300, 2) * 2 - 1
+    ds = dict(train_input=x, train_label=(x[:, :1] * x[:, 1:]).sin(), test_input=x, test_label=(x[:, :1] * x[:, 1:]).sin())
+    model = QKAN([2, 3, 1], reps=2, seed=0, preact_trainable=True, postact_weight_trainable=True).to("cuda")
+    model.device = "cuda"
+    opt = AdamThenLbfgs(model.parameters(), switch_at=3)
+    res = model.train_(ds, optimizer=opt, steps=6, verbose=False)
+    assert len(res["train_loss"]) == 6 and opt.lbfgs is not None
+    assert float(res["train_loss"][-1]) < float(res["train_loss"][0])
