@@ -302,3 +302,30 @@ def test_seeded_random_shapes_and_flags_vs_oracle():
             if k == "postact_bias" and p["postb"] is None:
                 continue
             assert nerr(g[k], g_ref[k]) <= TOL_F32, f"{label}: grad {k} err {nerr(g[k], g_ref[k]):.3e}"
+
+
+def test_grouped_parameters_with_empty_batch_and_bf16():
+    """Grouped theta / preacts: an empty batch gives zero gradients in the grouped shapes, and bfloat16
+    activations with bfloat16 (O,I) tensors stay inside the bf16 bound against the oracle."""
+    from qkan_b200 import functional as F
+
+    B, I, O, R, G = 96, 45, 33, 2, 4
+    p = random_problem(9, B, I, O, R, use_pb=True, base=True)
+    rng = np.random.default_rng(3)
+    p["theta"] = rng.uniform(-np.pi, np.pi, (G, R + 1, 2)).astype(np.float32)
+    p["pw"] = (1 + 0.2 * rng.standard_normal((G, R))).astype(np.float32)
+    p["pb"] = (0.2 * rng.standard_normal((G, R))).astype(np.float32)
+    cfg = dict(preact_trainable=True, fast_measure=True, use_postact_bias=True)
+    th, pw, pb, postw, postb, basew = (_dev(p[k]) for k in ("theta", "pw", "pb", "postw", "postb", "basew"))
+    g0 = F.layer_backward(torch.empty((0, I), device="cuda"), th, pw, pb, postw, postb, basew, None,
+                          torch.empty((0, O), device="cuda"), **cfg)
+    assert g0["theta"].shape == (G, R + 1, 2) and g0["preacts_weight"].shape == (G, R)
+    assert all(float(v.abs().max()) == 0.0 for k, v in g0.items() if v.numel())
+    for k in ("x", "gy", "postw", "postb", "basew"):  # the oracle sees the bf16-rounded values
+        p[k] = torch.as_tensor(p[k]).to(torch.bfloat16).float().numpy()
+    y, g = _run_cuda(p, cfg, io_dtype=torch.bfloat16, param_dtype=torch.bfloat16)
+    q = dict(p, **{k: expand_group(p[k], O, I) for k in ("theta", "pw", "pb")})
+    y_ref, g_ref = _run_oracle(q, cfg)
+    for k in ("theta", "preacts_weight", "preacts_bias"):
+        g_ref[k] = reduce_group(g_ref[k], G)
+    _check(y, g, y_ref, g_ref, TOL_BF16, "grouped bf16")
