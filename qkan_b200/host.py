@@ -28,6 +28,21 @@ from . import functional as qf
 from .parallel import GradBucket, layer_grad_shapes
 
 
+def chunk_spans(batch: int, n_chunks: int, row_align: int = 148 * 64):
+    """Row ranges ``[(begin, end), ...]`` of at most ``n_chunks`` chunks covering ``batch`` rows.
+
+    The chunk length is rounded up to a multiple of ``row_align`` (whole waves of CTAs) when the batch holds
+    at least two such units; the last chunk takes the remainder.
+    """
+    if batch <= 0:
+        return []
+    n_chunks = max(1, min(n_chunks, batch))
+    step = (batch + n_chunks - 1) // n_chunks
+    if row_align > 1 and batch >= 2 * row_align:
+        step = (step + row_align - 1) // row_align * row_align
+    return [(b, min(batch, b + step)) for b in range(0, batch, step)]
+
+
 class HostLayerPipeline:
     """Chunked, stream-overlapped ``y, grad_x, parameter gradients`` from host-resident ``x, grad_y``."""
 
@@ -38,11 +53,7 @@ class HostLayerPipeline:
         self.device = torch.device(device)
         self.cfg = dict(preact_trainable=preact_trainable, fast_measure=fast_measure,
                         use_postact_bias=use_postact_bias, ansatz=ansatz)
-        n_chunks = max(1, min(n_chunks, batch))
-        step = (batch + n_chunks - 1) // n_chunks
-        if row_align > 1 and batch >= 2 * row_align:  # whole waves per chunk; the last chunk takes the remainder
-            step = (step + row_align - 1) // row_align * row_align
-        self.spans = [(b, min(batch, b + step)) for b in range(0, batch, step)]
+        self.spans = chunk_spans(batch, n_chunks, row_align)
         dev = self.device
         self.dx = [torch.empty((e - b, in_dim), dtype=dtype, device=dev) for b, e in self.spans]
         self.dgy = [torch.empty((e - b, out_dim), dtype=dtype, device=dev) for b, e in self.spans]

@@ -143,3 +143,19 @@ def test_refine_copies_the_leading_circuit_layers_and_zeroes_the_rest():
     with pytest.raises(AssertionError):
         QKAN([3, 5, 2], reps=4).initialize_from_another_model(small)
     assert not big.initialize_parameters().layers[0].theta.any()
+
+
+def test_host_pipeline_chunks_cover_the_batch_in_whole_waves():
+    from qkan_b200.host import chunk_spans
+
+    wave = 148 * 64
+    spans = chunk_spans(65536, 3)
+    assert spans == [(0, 3 * wave), (3 * wave, 6 * wave), (6 * wave, 65536)]
+    assert chunk_spans(65536, 4) == [(0, 2 * wave), (2 * wave, 4 * wave), (4 * wave, 6 * wave), (6 * wave, 65536)]
+    assert chunk_spans(1000, 4, row_align=256) == [(0, 256), (256, 512), (512, 768), (768, 1000)]
+    assert chunk_spans(1000, 3) == [(0, 334), (334, 668), (668, 1000)]  # too small to align: equal chunks
+    assert chunk_spans(5, 8) == [(i, i + 1) for i in range(5)] and chunk_spans(0, 4) == []
+    for batch, n in ((1, 1), (9472, 2), (100000, 5), (65537, 3)):
+        s = chunk_spans(batch, n)
+        assert s[0][0] == 0 and s[-1][1] == batch and len(s) <= n
+        assert all(a[1] == b[0] for a, b in zip(s, s[1:]))
