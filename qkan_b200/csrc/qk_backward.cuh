@@ -92,7 +92,7 @@ __device__ __forceinline__ float edge_backward(const EdgeFwd<R>& e, float x, flo
 constexpr int kGyChunk = 8;  // outputs whose grad_y columns are staged together
 
 template <int R, bool FAST, typename IO, bool EDGES, int RU, bool PRECISE, bool OSLICE>
-__global__ void __launch_bounds__(256) backward_kernel(BwdArgs a) {
+__global__ void __launch_bounds__(256, R <= 3 ? 2 : 0) backward_kernel(BwdArgs a) {
     constexpr int NACC = acc_rows(R);
     // floats per tile row: 32 (x, grad_x) pairs; a pair is one 64-bit access
     constexpr int ROW = 64;

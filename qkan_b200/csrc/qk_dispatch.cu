@@ -87,7 +87,10 @@ BwdCfg choose_bwd_cfg(const QkDesc& d) {
         return slice(make(force_groups, force_rpg), force_osplit > 0 ? force_osplit : 1);
     // (row groups = warps per CTA, rows per group), largest tile first
     static const int cand[][2] = {{8, 32}, {8, 16}, {4, 32}, {4, 16}, {8, 8}, {2, 32}, {4, 8}, {2, 16}, {2, 8}, {1, 8}};
-    const int regs_est = rk > 8 ? 255 : 34 + 11 * rk;
+    // registers per thread as compiled: up to 3 repetitions the kernel is built for two CTAs of 256 threads per
+    // SM, which lets the compiler spend ~96 registers on scheduling (measured -2 % at 3 repetitions, -5 % at 1;
+    // longer circuits were 1-2 % faster with the compiler's own choice)
+    const int regs_est = rk > 8 ? 255 : (rk <= 3 ? 48 + 14 * rk : 34 + 11 * rk);
     const int ipad = round_up(d.in_dim, 32);
     // seconds per (row x 32 columns x output) on one SM: ~(28 R + 20) instructions at 0.72 IPC x 4 schedulers
     const double t_unit = (28.0 * rk + 20.0) / (4 * 0.72 * 1.965e9);
