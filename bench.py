@@ -56,10 +56,10 @@ VARIANTS = {"headline": "preacts trainable, fast readout, base term off",
 SM_COUNT, FP32_LANES, SFU_LANES, NOMINAL_GHZ = 148, 128, 16, 1.965
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one backward_kernel launch, from the ncu capture of a
-# 16384-row case (53.7 MB + 162.8 MB, backward tile pinned to the full batch's) scaled by 4 to the 65536-row
+# 16384-row case (52.2 MB + 161.6 MB, backward tile pinned to the full batch's) scaled by 4 to the 65536-row
 # batch; the traffic is proportional to the batch (activations and per-tile partials).
 # See profiles/forward_backward_kernels_batch16384.md.
-BACKWARD_DRAM_BYTES_PER_LAUNCH = 4 * (53_745_664 + 162_844_672)
+BACKWARD_DRAM_BYTES_PER_LAUNCH = 4 * (52_166_912 + 161_625_344)
 
 
 def issue_roofline_seconds(edges: float, reps: int, which: str, ghz: float = NOMINAL_GHZ,
