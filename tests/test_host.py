@@ -159,3 +159,13 @@ def test_host_pipeline_chunks_cover_the_batch_in_whole_waves():
         s = chunk_spans(batch, n)
         assert s[0][0] == 0 and s[-1][1] == batch and len(s) <= n
         assert all(a[1] == b[0] for a, b in zip(s, s[1:]))
+
+
+def test_host_thread_binding_is_a_no_op_without_a_gpu():
+    import os
+
+    from qkan_b200 import bind_host_thread_near_gpu
+
+    before = os.sched_getaffinity(0)
+    assert bind_host_thread_near_gpu(0) is None or isinstance(bind_host_thread_near_gpu(0), int)
+    assert os.sched_getaffinity(0) <= before  # never widens the mask; unchanged when NVML has no device
