@@ -24,7 +24,7 @@
 extern "C" {
 #endif
 
-#define QK_ABI_VERSION 3
+#define QK_ABI_VERSION 4
 
 enum QkDtype { QK_F32 = 0, QK_BF16 = 1 };
 
@@ -42,8 +42,10 @@ enum QkFlags {
     QK_FAST_MEASURE = 2u,     /* |a|-|b| readout; otherwise |a|^2-|b|^2 (torch_qc.py:261-277) */
     QK_USE_POSTACT_BIAS = 4u, /* add postact_bias before the weight (qkan.py:776-783) */
     QK_PRECISE_MATH = 8u      /* sin/cos/sqrt by the full-precision routines instead of the special-function
-                                 unit (float32 I/O only): ~1 ulp and smooth in the argument, as torch's own
-                                 sin/cos in the reference are; meant for small fits driven by LBFGS */
+                                 unit: ~1 ulp and smooth in the argument, as torch's own sin/cos in the
+                                 reference are; meant for small fits driven by LBFGS. Honoured for QK_F32
+                                 activations; with QK_BF16 activations the flag is accepted and has no effect
+                                 (bfloat16 rounding of x and y is four orders of magnitude coarser) */
 };
 
 enum QkError {
@@ -79,7 +81,8 @@ const char* qk_last_error(void);
 /*
  * Bytes of device scratch the forward / backward need for this problem.
  * The caller owns the scratch (any 256-byte aligned device allocation) and
- * may reuse it between calls on the same stream.
+ * may reuse it between calls on the same stream. The first qk_tables_bytes() bytes
+ * hold the prepared state described further down; the backward's share follows it.
  */
 size_t qk_forward_workspace_bytes(const QkDesc* desc);
 size_t qk_backward_workspace_bytes(const QkDesc* desc);
@@ -115,6 +118,37 @@ int qk_pz_backward(const QkDesc* desc, const void* x, const float* theta,
                    float* grad_preacts_weight, float* grad_preacts_bias,
                    float* grad_postact_weights, float* grad_postact_bias, float* grad_base_weight,
                    void* workspace, size_t workspace_bytes, void* cuda_stream);
+
+/*
+ * The same layer step with its set-up hoisted out, four launches in all (prepare, forward, backward, finish).
+ *
+ * qk_pz_forward and qk_pz_backward each begin with a set-up kernel that turns the parameters into per-edge
+ * constants (sin/cos of theta, merged phases, postact_weights * mask, the folded bias vector): work the
+ * reference redoes inside every CTA (src/qkan/csrc/cute_kernels.cu:96-140, its shared-memory trig cache).
+ * A caller that runs forward and backward with unchanged parameters - every training step does - can build
+ * that state once with qk_pz_prepare into a buffer of qk_tables_bytes() bytes (depends on in_dim, out_dim,
+ * reps, ansatz, flags, group; not on batch) and pass it to both *_prepared calls. The buffer is valid until a
+ * parameter value changes. qk_backward_scratch_bytes() is the backward's scratch without the tables.
+ * `with_base_term` must be non-zero exactly when qk_pz_prepare was given a base_weight.
+ * postact_weights / postact_bias / mask are read again by the backward's finishing kernel.
+ */
+size_t qk_tables_bytes(const QkDesc* desc);
+size_t qk_backward_scratch_bytes(const QkDesc* desc);
+
+int qk_pz_prepare(const QkDesc* desc, const float* theta, const float* preacts_weight,
+                  const float* preacts_bias, const void* postact_weights, const void* postact_bias,
+                  const void* base_weight, const void* mask, void* tables, size_t tables_bytes,
+                  void* cuda_stream);
+
+int qk_pz_forward_prepared(const QkDesc* desc, const void* x, const void* tables, size_t tables_bytes,
+                           int with_base_term, void* y, void* cuda_stream);
+
+int qk_pz_backward_prepared(const QkDesc* desc, const void* x, const void* tables, size_t tables_bytes,
+                            const void* postact_weights, const void* postact_bias, const void* mask,
+                            int with_base_term, const void* grad_y, void* grad_x, float* grad_theta,
+                            float* grad_preacts_weight, float* grad_preacts_bias,
+                            float* grad_postact_weights, float* grad_postact_bias, float* grad_base_weight,
+                            void* scratch, size_t scratch_bytes, void* cuda_stream);
 
 /*
  * Solver plug-in contract (src/qkan/solver/_base.py:29-51, call site
@@ -166,6 +200,23 @@ int qk_pz_forward_noalloc(const QkDesc* desc, const void* x, const float* theta,
                           const float* preacts_weight, const float* preacts_bias,
                           const void* postact_weights, const void* postact_bias,
                           const void* base_weight, const void* mask, void* y, void* cuda_stream);
+
+/*
+ * Developer overrides of the tile choice, process-wide; no counterpart in the reference (its batch-tile
+ * heuristic, src/qkan/_kernel_utils.py:18-31, is fixed). 0 restores the library's own choice. On first use the
+ * values are seeded once from the environment variables QK_BWD_GROUPS, QK_BWD_RPG, QK_BWD_RU, QK_BWD_OSPLIT,
+ * QK_NO_XTRIG and QK_DEBUG; the launch path itself never reads the environment. Workspace sizes depend on the
+ * tile choice: query them after setting an override, and do not change one between a size query and its call.
+ */
+enum QkDebugKey {
+    QK_DBG_BWD_GROUPS = 0, /* warps (row groups) per backward CTA; needs QK_DBG_BWD_RPG too */
+    QK_DBG_BWD_RPG = 1,    /* rows per group */
+    QK_DBG_BWD_RU = 2,     /* rows a thread keeps in flight (2 or 4) */
+    QK_DBG_BWD_OSPLIT = 3, /* output slices of the backward (grid.z) */
+    QK_DBG_NO_XTRIG = 4,   /* non-zero: frozen-preact forward uses the generic kernel */
+    QK_DBG_VERBOSE = 5     /* non-zero: print the chosen tiles to stderr */
+};
+void qk_debug_set(int key, int value);
 
 #ifdef __cplusplus
 }

@@ -9,7 +9,7 @@ import ctypes
 import os
 from ctypes import Structure, c_char_p, c_int, c_int32, c_size_t, c_uint32, c_void_p
 
-QK_ABI_VERSION = 3
+QK_ABI_VERSION = 4
 
 QK_F32 = 0
 QK_BF16 = 1
@@ -24,6 +24,8 @@ QK_PREACT_TRAINABLE = 1
 QK_FAST_MEASURE = 2
 QK_USE_POSTACT_BIAS = 4
 QK_PRECISE_MATH = 8
+
+QK_DBG_BWD_GROUPS, QK_DBG_BWD_RPG, QK_DBG_BWD_RU, QK_DBG_BWD_OSPLIT, QK_DBG_NO_XTRIG, QK_DBG_VERBOSE = range(6)
 
 QK_OK = 0
 QK_ERR_BAD_ARGUMENT = -1
@@ -44,6 +46,12 @@ SYMBOLS = {
     "qk_pz_backward": (c_int, [_P] * 17 + [_P, c_size_t, _P]),
     "qk_pz_postacts_forward": (c_int, [_P] * 6 + [_P, c_size_t, _P]),
     "qk_pz_postacts_backward": (c_int, [_P] * 10 + [_P, c_size_t, _P]),
+    "qk_tables_bytes": (c_size_t, [_P]),
+    "qk_backward_scratch_bytes": (c_size_t, [_P]),
+    "qk_pz_prepare": (c_int, [_P] * 8 + [_P, c_size_t, _P]),
+    "qk_pz_forward_prepared": (c_int, [_P, _P, _P, c_size_t, c_int, _P, _P]),
+    "qk_pz_backward_prepared": (c_int, [_P, _P, _P, c_size_t, _P, _P, _P, c_int] + [_P] * 8 + [_P, c_size_t, _P]),
+    "qk_debug_set": (None, [c_int, c_int]),
     "qk_noalloc_max_scratch_bytes": (c_size_t, []),
     "qk_noalloc_last_error": (c_char_p, []),
     "qk_pz_forward_noalloc": (c_int, [_P] * 10 + [_P]),

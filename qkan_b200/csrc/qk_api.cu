@@ -1,6 +1,7 @@
 // C ABI of the library (see include/qkan_b200.h): argument validation,
 // workspace carving and the kernel launch sequence. No torch types, no
-// allocation, no synchronisation.
+// allocation, no synchronisation. A layer step is four launches: set-up (tables + bias), forward,
+// backward, gradient finish (one more with the base term on, one more per sliced / grouped extra).
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
@@ -51,17 +52,23 @@ int check_desc(const QkDesc* d) {
 bool use_xtrig(const QkDesc& d) {
     const int rk = qk::compiled_reps(d.ansatz, d.reps);
     return d.ansatz == QK_ANSATZ_PZ && !(d.flags & QK_PREACT_TRAINABLE) && !(d.flags & QK_PRECISE_MATH) &&
-           rk >= 1 && rk <= 8 && !getenv("QK_NO_XTRIG");
+           rk >= 1 && rk <= 8 && !qk::debug_get(qk::kDbgNoXtrig);
 }
 
-struct Layout {
+// The prepared state of a layer: per-edge constant table, folded bias vector and, for the frozen-preact
+// forward, that kernel's own table. Depends on the layer's shape and flags only, not on the batch.
+struct Tables {
     int ipad;
-    size_t table_off, bias_off, colsum_off, partials_off, total;
-    size_t gtheta_off, gpw_off, gpb_off;  // per-edge gradients ahead of the group reduction (group > 0)
-    size_t gxpart_off;                    // grad_x shares of the output slices (BwdCfg::osplit > 1)
-    size_t basepart_off;                  // row-tile partials of grad_base_weight (base-term kernel)
+    bool xtrig;
+    size_t table_off, bias_off, tablex_off, total;
+};
+
+// Scratch of one backward call: per-tile column sums of grad_y, per-tile gradient partials, the base-term
+// kernel's partials, the grad_x shares of sliced launches, per-edge gradients ahead of a group reduction.
+struct Scratch {
+    qk::BwdCfg cfg;
     int base_tiles;
-    int ncolsplit;
+    size_t colpart_off, partials_off, basepart_off, gxpart_off, gtheta_off, gpw_off, gpb_off, total;
 };
 
 size_t theta_per_entry(const QkDesc& d) {
@@ -69,32 +76,36 @@ size_t theta_per_entry(const QkDesc& d) {
                                     : (d.ansatz == QK_ANSATZ_RPZ ? (size_t)d.reps + 1 : (size_t)d.reps);
 }
 
-Layout forward_layout(const QkDesc& d) {
-    Layout l{};
+Tables tables_layout(const QkDesc& d) {
+    Tables l{};
     l.ipad = qk::round_up(d.in_dim, 32);
+    l.xtrig = use_xtrig(d);
+    const size_t table =
+        qk::align256((size_t)d.out_dim * qk::table_stride(qk::compiled_reps(d.ansatz, d.reps)) * l.ipad * sizeof(float));
     l.table_off = 0;
-    size_t table = (size_t)d.out_dim * qk::table_stride(qk::compiled_reps(d.ansatz, d.reps)) * l.ipad * sizeof(float);
-    l.bias_off = qk::align256(table);
+    l.bias_off = table;
     l.total = l.bias_off + qk::align256((size_t)d.out_dim * sizeof(float));
+    if (l.xtrig) {
+        l.tablex_off = l.total;
+        l.total += table;
+    }
     return l;
 }
 
-Layout backward_layout(const QkDesc& d) {
-    Layout l = forward_layout(d);
-    qk::BwdCfg c = qk::choose_bwd_cfg(d);
-    l.ncolsplit = d.batch <= 0 ? 1 : (d.batch + 255) / 256;
-    if (l.ncolsplit > 64) l.ncolsplit = 64;
-    l.colsum_off = l.total;
-    l.partials_off = l.colsum_off + qk::align256((size_t)l.ncolsplit * d.out_dim * sizeof(float));
-    l.total = l.partials_off +
-              qk::align256((size_t)c.grid_b * d.out_dim * c.nacc * l.ipad * sizeof(float));
+Scratch scratch_layout(const QkDesc& d) {
+    Scratch l{};
+    const int ipad = qk::round_up(d.in_dim, 32);
+    l.cfg = qk::choose_bwd_cfg(d);
+    l.colpart_off = 0;
+    l.partials_off = qk::align256((size_t)l.cfg.grid_b * d.out_dim * sizeof(float));
+    l.total = l.partials_off + qk::align256((size_t)l.cfg.grid_b * d.out_dim * l.cfg.nacc * ipad * sizeof(float));
     const int base_tb = qk::base_rows_per_cta(d.batch, d.in_dim);
     l.base_tiles = (d.batch + base_tb - 1) / base_tb;
     l.basepart_off = l.total;
-    l.total += qk::align256((size_t)l.base_tiles * d.out_dim * l.ipad * sizeof(float));
-    if (c.osplit > 1) {
+    l.total += qk::align256((size_t)l.base_tiles * d.out_dim * ipad * sizeof(float));
+    if (l.cfg.osplit > 1) {
         l.gxpart_off = l.total;
-        l.total += qk::align256((size_t)c.osplit * d.batch * d.in_dim * sizeof(float));
+        l.total += qk::align256((size_t)l.cfg.osplit * d.batch * d.in_dim * sizeof(float));
     }
     if (d.group > 0) {
         const size_t nE = (size_t)d.out_dim * d.in_dim;
@@ -107,38 +118,34 @@ Layout backward_layout(const QkDesc& d) {
 }
 
 bool empty(const QkDesc& d) { return d.batch == 0 || d.in_dim == 0 || d.out_dim == 0; }
+// the prepared state has no batch axis: only a layer without edges has nothing to prepare
+bool no_edges(const QkDesc& d) { return d.in_dim == 0 || d.out_dim == 0; }
 
 int cuda_fail(cudaError_t e, const char* what) {
     return fail(QK_ERR_LAUNCH, "%s: %s", what, cudaGetErrorString(e));
 }
 
-int run_forward(const QkDesc* desc, const void* x, const float* theta, const float* pw,
-                const float* pb, const void* postw, const void* postb, const void* basew,
-                const void* mask, void* y, void* postacts, void* ws, size_t ws_bytes,
-                cudaStream_t st) {
+int check_buffer(const void* p, size_t have, size_t need, const char* what) {
+    if (!p || have < need)
+        return fail(QK_ERR_WORKSPACE, "%s too small: need %zu bytes, got %zu", what, need, p ? have : (size_t)0);
+    if ((uintptr_t)p % 256) return fail(QK_ERR_WORKSPACE, "%s must be 256-byte aligned", what);
+    return QK_OK;
+}
+
+// `edges`: solver-contract mode (no epilogue: weight 1, no bias, no base term, no mask)
+int run_prepare(const QkDesc* desc, const float* theta, const float* pw, const float* pb, const void* postw,
+                const void* postb, const void* basew, const void* mask, bool edges, void* tables,
+                size_t tables_bytes, cudaStream_t st) {
     int rc = check_desc(desc);
     if (rc) return rc;
     const QkDesc& d = *desc;
-    const bool edges = postacts != nullptr;
-    if (empty(d)) {
-        // y (B,O) of an in_dim == 0 layer is all zeros; the other empty shapes have no output
-        if (!edges && d.in_dim == 0 && d.batch > 0 && d.out_dim > 0) {
-            size_t es = d.io_dtype == QK_BF16 ? 2 : 4;
-            cudaError_t e = cudaMemsetAsync(y, 0, (size_t)d.batch * d.out_dim * es, st);
-            if (e != cudaSuccess) return cuda_fail(e, "memset y");
-        }
-        return QK_OK;
-    }
-    if (!x || !theta || !pw || !pb) return fail(QK_ERR_BAD_ARGUMENT, "x/theta/preacts pointer is NULL");
-    if (!edges && (!postw || !y)) return fail(QK_ERR_BAD_ARGUMENT, "postact_weights or y is NULL");
-    Layout l = forward_layout(d);
-    if (!ws || ws_bytes < l.total)
-        return fail(QK_ERR_WORKSPACE, "workspace too small: need %zu bytes, got %zu", l.total, ws_bytes);
-    if ((uintptr_t)ws % 256)
-        return fail(QK_ERR_WORKSPACE, "workspace must be 256-byte aligned");
-    char* wsb = static_cast<char*>(ws);
-    const bool has_base = !edges && basew != nullptr;
-
+    if (no_edges(d)) return QK_OK;
+    if (!theta || !pw || !pb) return fail(QK_ERR_BAD_ARGUMENT, "theta/preacts pointer is NULL");
+    if (!edges && !postw) return fail(QK_ERR_BAD_ARGUMENT, "postact_weights is NULL");
+    const Tables l = tables_layout(d);
+    rc = check_buffer(tables, tables_bytes, l.total, "tables");
+    if (rc) return rc;
+    char* tb = static_cast<char*>(tables);
     qk::PrepArgs p{};
     p.in_dim = d.in_dim;
     p.out_dim = d.out_dim;
@@ -148,20 +155,44 @@ int run_forward(const QkDesc* desc, const void* x, const float* theta, const flo
     p.ipad = l.ipad;
     p.flags = d.flags;
     p.param_dtype = d.param_dtype;
+    p.group = d.group;
     p.theta = theta;
     p.pw = pw;
     p.pb = pb;
     p.postw = edges ? nullptr : postw;
     p.postb = edges ? nullptr : postb;
-    p.basew = has_base ? basew : nullptr;
+    p.basew = edges ? nullptr : basew;
     p.mask = edges ? nullptr : mask;
-    p.table = reinterpret_cast<float*>(wsb + l.table_off);
-    p.bias = edges ? nullptr : reinterpret_cast<float*>(wsb + l.bias_off);
-    p.group = d.group;
-    const bool xtrig = use_xtrig(d);
-    p.xtrig = xtrig;
+    p.table = reinterpret_cast<float*>(tb + l.table_off);
+    p.table_x = l.xtrig ? reinterpret_cast<float*>(tb + l.tablex_off) : nullptr;
+    p.bias = edges ? nullptr : reinterpret_cast<float*>(tb + l.bias_off);
     cudaError_t e = qk::launch_prep(p, st);
     if (e != cudaSuccess) return cuda_fail(e, "prep launch");
+    return QK_OK;
+}
+
+int run_forward_prepared(const QkDesc* desc, const void* x, const void* tables, size_t tables_bytes,
+                         bool has_base, void* y, void* postacts, cudaStream_t st) {
+    int rc = check_desc(desc);
+    if (rc) return rc;
+    const QkDesc& d = *desc;
+    const bool edges = postacts != nullptr;
+    if (empty(d)) {
+        // y (B,O) of an in_dim == 0 layer is all zeros; the other empty shapes have no output
+        if (!edges && d.in_dim == 0 && d.batch > 0 && d.out_dim > 0 && y) {
+            size_t es = d.io_dtype == QK_BF16 ? 2 : 4;
+            cudaError_t e = cudaMemsetAsync(y, 0, (size_t)d.batch * d.out_dim * es, st);
+            if (e != cudaSuccess) return cuda_fail(e, "memset y");
+        }
+        return QK_OK;
+    }
+    if (!x) return fail(QK_ERR_BAD_ARGUMENT, "x is NULL");
+    if (!edges && !y) return fail(QK_ERR_BAD_ARGUMENT, "y is NULL");
+    const Tables l = tables_layout(d);
+    rc = check_buffer(tables, tables_bytes, l.total, "tables");
+    if (rc) return rc;
+    const char* tb = static_cast<const char*>(tables);
+    has_base = has_base && !edges;
 
     qk::FwdArgs f{};
     f.batch = d.batch;
@@ -169,26 +200,27 @@ int run_forward(const QkDesc* desc, const void* x, const float* theta, const flo
     f.out_dim = d.out_dim;
     f.ipad = l.ipad;
     f.precise = (d.flags & QK_PRECISE_MATH) != 0;
-    f.xtrig = xtrig;
-    f.cfg = qk::choose_fwd_cfg(d, edges, has_base, xtrig);
-    if (getenv("QK_DEBUG"))
+    f.xtrig = l.xtrig;
+    f.cfg = qk::choose_fwd_cfg(d, edges, has_base, l.xtrig);
+    if (qk::debug_get(qk::kDbgVerbose))
         fprintf(stderr, "[qk] forward B=%d I=%d O=%d R=%d: tile %d rows x %d outputs, grid %d x %d, smem %zu\n",
                 d.batch, d.in_dim, d.out_dim, d.reps, f.cfg.tb, f.cfg.ot, f.cfg.grid_b, f.cfg.grid_o, f.cfg.smem);
     f.x = x;
-    f.table = p.table;
-    f.bias = p.bias;
+    f.table = reinterpret_cast<const float*>(tb + (l.xtrig ? l.tablex_off : l.table_off));
+    f.bias = reinterpret_cast<const float*>(tb + l.bias_off);
     f.y = y;
     f.postacts = postacts;
-    e = qk::launch_forward(f, p.rk, (d.flags & QK_FAST_MEASURE) != 0, d.io_dtype, has_base, st);
+    cudaError_t e = qk::launch_forward(f, qk::compiled_reps(d.ansatz, d.reps), (d.flags & QK_FAST_MEASURE) != 0,
+                                       d.io_dtype, has_base, st);
     if (e != cudaSuccess) return cuda_fail(e, "forward launch");
     return QK_OK;
 }
 
-int run_backward(const QkDesc* desc, const void* x, const float* theta, const float* pw,
-                 const float* pb, const void* postw, const void* postb, const void* basew,
-                 const void* mask, const void* gy, const void* gpostacts, void* gx, float* gtheta,
-                 float* gpw, float* gpb, float* gpostw, float* gpostb, float* gbasew, void* ws,
-                 size_t ws_bytes, cudaStream_t st) {
+int run_backward_prepared(const QkDesc* desc, const void* x, const void* tables, size_t tables_bytes,
+                          const void* postw, const void* postb, const void* mask, bool has_base,
+                          const void* gy, const void* gpostacts, void* gx, float* gtheta, float* gpw,
+                          float* gpb, float* gpostw, float* gpostb, float* gbasew, void* scratch,
+                          size_t scratch_bytes, cudaStream_t st) {
     int rc = check_desc(desc);
     if (rc) return rc;
     const QkDesc& d = *desc;
@@ -209,66 +241,43 @@ int run_backward(const QkDesc* desc, const void* x, const float* theta, const fl
         if (e != cudaSuccess) return cuda_fail(e, "memset gradients");
         return QK_OK;
     }
-    if (!x || !theta || !pw || !pb) return fail(QK_ERR_BAD_ARGUMENT, "x/theta/preacts pointer is NULL");
+    if (!x) return fail(QK_ERR_BAD_ARGUMENT, "x is NULL");
     if (!edges && (!postw || !gy)) return fail(QK_ERR_BAD_ARGUMENT, "postact_weights or grad_y is NULL");
-    const bool has_base = !edges && basew != nullptr;
-    Layout l = backward_layout(d);
-    if (!ws || ws_bytes < l.total)
-        return fail(QK_ERR_WORKSPACE, "workspace too small: need %zu bytes, got %zu", l.total, ws_bytes);
-    if ((uintptr_t)ws % 256)
-        return fail(QK_ERR_WORKSPACE, "workspace must be 256-byte aligned");
-    char* wsb = static_cast<char*>(ws);
-
-    qk::PrepArgs p{};
-    p.in_dim = d.in_dim;
-    p.out_dim = d.out_dim;
-    p.reps = d.reps;
-    p.rk = qk::compiled_reps(d.ansatz, d.reps);
-    p.ansatz = d.ansatz;
-    p.ipad = l.ipad;
-    p.flags = d.flags;
-    p.param_dtype = d.param_dtype;
-    p.theta = theta;
-    p.pw = pw;
-    p.pb = pb;
-    p.postw = edges ? nullptr : postw;
-    p.postb = edges ? nullptr : postb;
-    p.basew = has_base ? basew : nullptr;
-    p.mask = edges ? nullptr : mask;
-    p.table = reinterpret_cast<float*>(wsb + l.table_off);
-    p.bias = nullptr;
-    p.xtrig = 0;
-    p.group = d.group;
-    cudaError_t e = qk::launch_prep(p, st);
-    if (e != cudaSuccess) return cuda_fail(e, "prep launch");
+    has_base = has_base && !edges;
+    const Tables tl = tables_layout(d);
+    rc = check_buffer(tables, tables_bytes, tl.total, "tables");
+    if (rc) return rc;
+    const Scratch l = scratch_layout(d);
+    rc = check_buffer(scratch, scratch_bytes, l.total, "workspace");
+    if (rc) return rc;
+    const float* table = reinterpret_cast<const float*>(static_cast<const char*>(tables) + tl.table_off);
+    char* wsb = static_cast<char*>(scratch);
+    const int rk = qk::compiled_reps(d.ansatz, d.reps);
 
     const bool use_pb = !edges && (d.flags & QK_USE_POSTACT_BIAS) && postb;
-    float* colsum = reinterpret_cast<float*>(wsb + l.colsum_off);
     const bool need_colsum = use_pb && (gpostw || gpostb);
-    if (need_colsum) {
-        e = qk::launch_colsum(gy, d.io_dtype, d.batch, d.out_dim, l.ncolsplit, colsum, st);
-        if (e != cudaSuccess) return cuda_fail(e, "colsum launch");
-    }
+    float* colpart = reinterpret_cast<float*>(wsb + l.colpart_off);
 
     qk::BwdArgs b{};
     b.batch = d.batch;
     b.in_dim = d.in_dim;
     b.out_dim = d.out_dim;
-    b.ipad = l.ipad;
+    b.ipad = tl.ipad;
     b.precise = (d.flags & QK_PRECISE_MATH) != 0;
-    b.cfg = qk::choose_bwd_cfg(d);
-    if (getenv("QK_DEBUG"))
+    b.cfg = l.cfg;
+    if (qk::debug_get(qk::kDbgVerbose))
         fprintf(stderr, "[qk] backward B=%d I=%d O=%d R=%d: %d groups x %d rows, grid %d x %d x %d output slices of %d, smem %zu, ru %d\n",
                 d.batch, d.in_dim, d.out_dim, d.reps, b.cfg.groups, b.cfg.rpg, b.cfg.grid_b, b.cfg.grid_i,
                 b.cfg.osplit, b.cfg.ochunk, b.cfg.smem, b.cfg.ru);
     b.x = x;
     b.gy = gy;
     b.gpostacts = gpostacts;
-    b.table = p.table;
+    b.table = table;
     b.gx = gx;
     b.gx_part = b.cfg.osplit > 1 ? reinterpret_cast<float*>(wsb + l.gxpart_off) : nullptr;
     b.partials = reinterpret_cast<float*>(wsb + l.partials_off);
-    e = qk::launch_backward(b, p.rk, (d.flags & QK_FAST_MEASURE) != 0, d.io_dtype, st);
+    b.colpart = need_colsum ? colpart : nullptr;
+    cudaError_t e = qk::launch_backward(b, rk, (d.flags & QK_FAST_MEASURE) != 0, d.io_dtype, st);
     if (e != cudaSuccess) return cuda_fail(e, "backward launch");
     if (gx && b.cfg.osplit > 1) {
         e = qk::launch_sum_gx(b.gx_part, gx, d.io_dtype, (size_t)d.batch * d.in_dim, b.cfg.osplit, st);
@@ -282,12 +291,12 @@ int run_backward(const QkDesc* desc, const void* x, const float* theta, const fl
         ba.batch = d.batch;
         ba.in_dim = d.in_dim;
         ba.out_dim = d.out_dim;
-        ba.ipad = l.ipad;
-        ba.ks = qk::table_stride(p.rk);
-        ba.bw_row = qk::t_bw(p.rk);
+        ba.ipad = tl.ipad;
+        ba.ks = qk::table_stride(rk);
+        ba.bw_row = qk::t_bw(rk);
         ba.x = x;
         ba.gy = gy;
-        ba.table = p.table;
+        ba.table = table;
         ba.gx = gx;
         ba.partials = gbasew ? base_partials : nullptr;
         e = qk::launch_base_backward(ba, d.io_dtype, st);
@@ -299,18 +308,17 @@ int run_backward(const QkDesc* desc, const void* x, const float* theta, const fl
         f.in_dim = d.in_dim;
         f.out_dim = d.out_dim;
         f.reps = d.reps;
-        f.rk = p.rk;
+        f.rk = rk;
         f.ansatz = d.ansatz;
-        f.ipad = l.ipad;
+        f.ipad = tl.ipad;
         f.nacc = b.cfg.nacc;
         f.ntiles = b.cfg.grid_b;
-        f.ncolsplit = l.ncolsplit;
         f.base_tiles = has_base && gbasew ? l.base_tiles : 0;
         f.base_partials = f.base_tiles ? base_partials : nullptr;
         f.flags = d.flags;
         f.param_dtype = d.param_dtype;
         f.partials = b.partials;
-        f.colsum = need_colsum ? colsum : nullptr;
+        f.colpart = need_colsum ? colpart : nullptr;
         f.postw = edges ? nullptr : postw;
         f.postb = edges ? nullptr : postb;
         f.mask = edges ? nullptr : mask;
@@ -337,6 +345,48 @@ int run_backward(const QkDesc* desc, const void* x, const float* theta, const fl
     return QK_OK;
 }
 
+// one-workspace entry points: [tables | scratch]
+int run_forward(const QkDesc* desc, const void* x, const float* theta, const float* pw, const float* pb,
+                const void* postw, const void* postb, const void* basew, const void* mask, void* y,
+                void* postacts, void* ws, size_t ws_bytes, cudaStream_t st) {
+    int rc = check_desc(desc);
+    if (rc) return rc;
+    const bool edges = postacts != nullptr;
+    if (!empty(*desc)) {
+        if (!x || !theta || !pw || !pb) return fail(QK_ERR_BAD_ARGUMENT, "x/theta/preacts pointer is NULL");
+        if (!edges && (!postw || !y)) return fail(QK_ERR_BAD_ARGUMENT, "postact_weights or y is NULL");
+        rc = check_buffer(ws, ws_bytes, tables_layout(*desc).total, "workspace");
+        if (rc) return rc;
+        rc = run_prepare(desc, theta, pw, pb, postw, postb, basew, mask, edges, ws, ws_bytes, st);
+        if (rc) return rc;
+    }
+    return run_forward_prepared(desc, x, ws, ws_bytes, basew != nullptr, y, postacts, st);
+}
+
+int run_backward(const QkDesc* desc, const void* x, const float* theta, const float* pw, const float* pb,
+                 const void* postw, const void* postb, const void* basew, const void* mask, const void* gy,
+                 const void* gpostacts, void* gx, float* gtheta, float* gpw, float* gpb, float* gpostw,
+                 float* gpostb, float* gbasew, void* ws, size_t ws_bytes, cudaStream_t st) {
+    int rc = check_desc(desc);
+    if (rc) return rc;
+    const bool edges = gpostacts != nullptr;
+    size_t toff = 0;
+    if (!empty(*desc)) {
+        if (!x || !theta || !pw || !pb) return fail(QK_ERR_BAD_ARGUMENT, "x/theta/preacts pointer is NULL");
+        if (!edges && (!postw || !gy)) return fail(QK_ERR_BAD_ARGUMENT, "postact_weights or grad_y is NULL");
+        toff = tables_layout(*desc).total;
+        const size_t need = toff + scratch_layout(*desc).total;
+        rc = check_buffer(ws, ws_bytes, need, "workspace");
+        if (rc) return rc;
+        rc = run_prepare(desc, theta, pw, pb, postw, postb, basew, mask, edges, ws, toff, st);
+        if (rc) return rc;
+    }
+    return run_backward_prepared(desc, x, ws, toff, postw, postb, mask, basew != nullptr, gy, gpostacts, gx,
+                                 gtheta, gpw, gpb, gpostw, gpostb, gbasew,
+                                 ws ? static_cast<char*>(ws) + toff : nullptr, ws_bytes >= toff ? ws_bytes - toff : 0,
+                                 st);
+}
+
 }  // namespace
 
 extern "C" {
@@ -348,14 +398,50 @@ const char* qk_last_error(void) { return g_err; }
 size_t qk_forward_workspace_bytes(const QkDesc* desc) {
     if (check_desc(desc)) return 0;
     if (empty(*desc)) return 256;
-    return forward_layout(*desc).total;
+    return tables_layout(*desc).total;
 }
 
 size_t qk_backward_workspace_bytes(const QkDesc* desc) {
     if (check_desc(desc)) return 0;
     if (empty(*desc)) return 256;
-    return backward_layout(*desc).total;
+    return tables_layout(*desc).total + scratch_layout(*desc).total;
 }
+
+size_t qk_tables_bytes(const QkDesc* desc) {
+    if (check_desc(desc)) return 0;
+    if (no_edges(*desc)) return 256;
+    return tables_layout(*desc).total;
+}
+
+size_t qk_backward_scratch_bytes(const QkDesc* desc) {
+    if (check_desc(desc)) return 0;
+    if (empty(*desc)) return 256;
+    return scratch_layout(*desc).total;
+}
+
+int qk_pz_prepare(const QkDesc* desc, const float* theta, const float* pw, const float* pb,
+                  const void* postw, const void* postb, const void* basew, const void* mask, void* tables,
+                  size_t tables_bytes, void* stream) {
+    return run_prepare(desc, theta, pw, pb, postw, postb, basew, mask, false, tables, tables_bytes,
+                       static_cast<cudaStream_t>(stream));
+}
+
+int qk_pz_forward_prepared(const QkDesc* desc, const void* x, const void* tables, size_t tables_bytes,
+                           int with_base_term, void* y, void* stream) {
+    return run_forward_prepared(desc, x, tables, tables_bytes, with_base_term != 0, y, nullptr,
+                                static_cast<cudaStream_t>(stream));
+}
+
+int qk_pz_backward_prepared(const QkDesc* desc, const void* x, const void* tables, size_t tables_bytes,
+                            const void* postw, const void* postb, const void* mask, int with_base_term,
+                            const void* gy, void* gx, float* gtheta, float* gpw, float* gpb, float* gpostw,
+                            float* gpostb, float* gbasew, void* scratch, size_t scratch_bytes, void* stream) {
+    return run_backward_prepared(desc, x, tables, tables_bytes, postw, postb, mask, with_base_term != 0, gy,
+                                 nullptr, gx, gtheta, gpw, gpb, gpostw, gpostb, gbasew, scratch, scratch_bytes,
+                                 static_cast<cudaStream_t>(stream));
+}
+
+void qk_debug_set(int key, int value) { qk::debug_set(key, value); }
 
 int qk_pz_forward(const QkDesc* desc, const void* x, const float* theta, const float* pw,
                   const float* pb, const void* postw, const void* postb, const void* basew,

@@ -91,6 +91,21 @@ __device__ __forceinline__ float edge_backward(const EdgeFwd<R>& e, float x, flo
 
 constexpr int kGyChunk = 8;  // outputs whose grad_y columns are staged together
 
+// Column sums of one batch tile's staged grad_y rows (the postact-bias terms need sum_b grad_y[b,o]): taken by
+// the CTAs of column block 0 only, one warp per output, lane-strided partial sums and a shuffle tree (fixed
+// order); finish_grads adds the tiles in order. Kept out of line so that the hot loop's register allocation
+// is the same with and without it.
+static __device__ __noinline__ void tile_column_sums(float* __restrict__ dst, const float* gy_s, int nch, int groups, int tb) {
+    const int lane = threadIdx.x % kWarp, grp = threadIdx.x / kWarp;
+    for (int c = grp; c < nch; c += groups) {
+        float s = 0.f;
+        for (int r = lane; r < tb; r += kWarp) s += gy_s[c * tb + r];
+#pragma unroll
+        for (int d = 16; d >= 1; d >>= 1) s += __shfl_xor_sync(0xffffffffu, s, d);
+        if (lane == 0) dst[c] = s;
+    }
+}
+
 template <int R, bool FAST, typename IO, bool EDGES, int RU, bool PRECISE, bool OSLICE>
 __global__ void __launch_bounds__(256, R <= 3 ? 2 : 0) backward_kernel(BwdArgs a) {
     constexpr int NACC = acc_rows(R);
@@ -155,6 +170,8 @@ __global__ void __launch_bounds__(256, R <= 3 ? 2 : 0) backward_kernel(BwdArgs a
                 }
             }
             __syncthreads();
+            if (a.colpart && blockIdx.y == 0)
+                tile_column_sums(a.colpart + (size_t)bt * a.out_dim + oc, gy_s, nch, groups, tb);
         }
         for (int ol = 0; ol < nch; ++ol) {
             const int o = oc + ol;
@@ -238,21 +255,32 @@ __global__ void __launch_bounds__(256, R <= 3 ? 2 : 0) backward_kernel(BwdArgs a
 
 template <int R, bool FAST, typename IO, bool EDGES>
 static cudaError_t launch_bwd_t(const BwdArgs& a, cudaStream_t st) {
+    // variant 0 / 1: four / two rows in flight; 2: full-precision math; 3 / 4: sliced outputs (plain / full precision)
+    int variant = a.cfg.ru == 4 ? 0 : 1;
     auto kern = a.cfg.ru == 4 ? backward_kernel<R, FAST, IO, EDGES, 4, false, false>
                               : backward_kernel<R, FAST, IO, EDGES, 2, false, false>;
     if constexpr (std::is_same<IO, float>::value) {  // the full-precision variant exists for float32 I/O
-        if (a.precise) kern = backward_kernel<R, FAST, IO, EDGES, 2, true, false>;
+        if (a.precise) {
+            kern = backward_kernel<R, FAST, IO, EDGES, 2, true, false>;
+            variant = 2;
+        }
     }
     if (a.cfg.osplit > 1) {
         // sliced outputs: one row-interleave per repetition count (rows per group are multiples of 4)
         constexpr int RU_S = (R > 8) ? 2 : 4;
         kern = backward_kernel<R, FAST, IO, EDGES, RU_S, false, true>;
+        variant = 3;
         if constexpr (std::is_same<IO, float>::value) {
-            if (a.precise) kern = backward_kernel<R, FAST, IO, EDGES, 2, true, true>;
+            if (a.precise) {
+                kern = backward_kernel<R, FAST, IO, EDGES, 2, true, true>;
+                variant = 4;
+            }
         }
     }
-    cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           (int)a.cfg.smem);
+    // Every instantiation is opted in to the tile choosers' shared-memory cap once per device, not per launch:
+    // host threads launching different shapes of one instantiation would otherwise race on the attribute.
+    static unsigned long long opted_in[5] = {0, 0, 0, 0, 0};
+    cudaError_t err = opt_in_smem(kern, &opted_in[variant]);
     if (err != cudaSuccess) return err;
     dim3 grid(a.cfg.grid_b, a.cfg.grid_i, a.cfg.osplit);
     kern<<<grid, a.cfg.groups * kWarp, a.cfg.smem, st>>>(a);

@@ -1,7 +1,9 @@
 // Tile-shape selection and the dispatch on the repetition count. The kernels
 // themselves are instantiated once per R in qk_forward_inst.cu / qk_backward_inst.cu.
+#include <atomic>
 #include <cstdlib>
 #include <initializer_list>
+#include <mutex>
 
 #include "qk_kernels.cuh"
 
@@ -9,10 +11,34 @@ namespace qk {
 
 constexpr int kGyChunkHost = 8;  // must match kGyChunk of the backward kernel
 
-// Developer tuning knob: integer environment override, read once per process.
-static int tune_int(const char* name, int dflt) {
-    const char* v = getenv(name);
-    return v && *v ? atoi(v) : dflt;
+// Developer overrides of the tile choice (0 = none). They are process-wide values set through qk_debug_set;
+// the first use seeds them, once, from the environment variables of the same names (QK_BWD_GROUPS, QK_BWD_RPG,
+// QK_BWD_RU, QK_BWD_OSPLIT, QK_NO_XTRIG, QK_DEBUG), so the launch path itself never reads the environment.
+static std::atomic<int> g_debug[kDbgCount];
+static std::once_flag g_debug_once;
+
+static void debug_seed() {
+    static const char* const names[kDbgCount] = {"QK_BWD_GROUPS", "QK_BWD_RPG", "QK_BWD_RU",
+                                                 "QK_BWD_OSPLIT", "QK_NO_XTRIG", "QK_DEBUG"};
+    for (int k = 0; k < kDbgCount; ++k) {
+        const char* v = getenv(names[k]);
+        g_debug[k].store(v && *v ? (atoi(v) != 0 ? atoi(v) : 1) : 0, std::memory_order_relaxed);
+    }
+}
+
+int debug_get(int key) {
+    std::call_once(g_debug_once, debug_seed);
+    return key >= 0 && key < kDbgCount ? g_debug[key].load(std::memory_order_relaxed) : 0;
+}
+
+void debug_set(int key, int value) {
+    std::call_once(g_debug_once, debug_seed);
+    if (key >= 0 && key < kDbgCount) g_debug[key].store(value, std::memory_order_relaxed);
+}
+
+static int tune_int(int key, int dflt) {
+    const int v = debug_get(key);
+    return v > 0 ? v : dflt;
 }
 
 template <int R>
@@ -69,7 +95,7 @@ BwdCfg choose_bwd_cfg(const QkDesc& d) {
     const int rk = compiled_reps(d.ansatz, d.reps);
     const int nacc = acc_rows(rk);
     const int grid_i = (d.in_dim + 31) / 32;
-    const int ru = tune_int("QK_BWD_RU", rk > 8 ? 2 : 4);  // long circuits: fewer rows in flight, no spills
+    const int ru = tune_int(kDbgBwdRu, rk > 8 ? 2 : 4);  // long circuits: fewer rows in flight, no spills
     auto make = [&](int groups, int rpg) {
         const int tb = groups * rpg;
         size_t smem = (size_t)tb * 32 * 4 * 2 + (size_t)kGyChunkHost * tb * 4 +
@@ -81,8 +107,8 @@ BwdCfg choose_bwd_cfg(const QkDesc& d) {
         c.osplit = (d.out_dim + c.ochunk - 1) / c.ochunk;
         return c;
     };
-    const int force_groups = tune_int("QK_BWD_GROUPS", 0), force_rpg = tune_int("QK_BWD_RPG", 0);
-    const int force_osplit = tune_int("QK_BWD_OSPLIT", 0);
+    const int force_groups = tune_int(kDbgBwdGroups, 0), force_rpg = tune_int(kDbgBwdRpg, 0);
+    const int force_osplit = tune_int(kDbgBwdOsplit, 0);
     if (force_groups > 0 && force_rpg > 0)  // developer override
         return slice(make(force_groups, force_rpg), force_osplit > 0 ? force_osplit : 1);
     // (row groups = warps per CTA, rows per group), largest tile first

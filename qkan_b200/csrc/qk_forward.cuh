@@ -133,15 +133,23 @@ __global__ void __launch_bounds__(512) forward_kernel(FwdArgs a) {
 
 template <int R, bool FAST, typename IO, bool BASE, bool EDGES>
 static cudaError_t launch_fwd_t(const FwdArgs& a, cudaStream_t st) {
+    int variant = 0;  // 0: special-function unit, 1: full-precision math, 2: frozen-preact form
     auto kern = forward_kernel<R, FAST, IO, BASE, EDGES, false, false>;
     if constexpr (std::is_same<IO, float>::value) {  // the full-precision variant exists for float32 I/O
-        if (a.precise) kern = forward_kernel<R, FAST, IO, BASE, EDGES, true, false>;
+        if (a.precise) {
+            kern = forward_kernel<R, FAST, IO, BASE, EDGES, true, false>;
+            variant = 1;
+        }
     }
     if constexpr (R >= 1 && R <= 8) {  // frozen-preact form (no identity padding possible beyond 8)
-        if (a.xtrig) kern = forward_kernel<R, FAST, IO, BASE, EDGES, false, true>;
+        if (a.xtrig) {
+            kern = forward_kernel<R, FAST, IO, BASE, EDGES, false, true>;
+            variant = 2;
+        }
     }
-    cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           (int)a.cfg.smem);
+    // opted in to the tile chooser's shared-memory cap once per device (see the backward launcher)
+    static unsigned long long opted_in[3] = {0, 0, 0};
+    cudaError_t err = opt_in_smem(kern, &opted_in[variant]);
     if (err != cudaSuccess) return err;
     dim3 grid(a.cfg.grid_b, a.cfg.grid_o);
     kern<<<grid, a.cfg.threads, a.cfg.smem, st>>>(a);

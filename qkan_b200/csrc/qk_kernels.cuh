@@ -9,7 +9,6 @@ struct PrepArgs {
     int in_dim, out_dim, reps, ipad;
     int rk;      // compiled_reps(ansatz, reps): the table is laid out for this repetition count
     int ansatz;  // QkAnsatz
-    int xtrig;   // frozen-preact forward: rows (pw_l, c_l) hold (cos c_l, sin c_l) instead
     int group;   // > 0: theta / preacts are grouped, edge (o,i) reads entry i % group
     unsigned flags;
     int param_dtype;
@@ -20,19 +19,20 @@ struct PrepArgs {
     const void* postb;
     const void* basew;
     const void* mask;
-    float* table;
-    float* bias;  // nullptr => not computed
+    float* table;    // generic table (backward, and every forward but the frozen-preact one)
+    float* table_x;  // frozen-preact forward's table: rows (pw_l, c_l) hold (cos c_l, sin c_l); nullptr => not wanted
+    float* bias;     // nullptr => not computed
 };
 
 struct FinishArgs {
-    int in_dim, out_dim, reps, ipad, nacc, ntiles, ncolsplit;
+    int in_dim, out_dim, reps, ipad, nacc, ntiles;
     int base_tiles;               // row tiles of the base-term kernel (0: no base term)
     const float* base_partials;   // [base_tiles][out_dim][ipad] partial sums of grad_base_weight
     int rk, ansatz;
     unsigned flags;
     int param_dtype;
     const float* partials;
-    const float* colsum;
+    const float* colpart;  // [ntiles][out_dim] per-tile column sums of grad_y (nullptr: postact-bias terms off)
     const void* postw;
     const void* postb;
     const void* mask;
@@ -89,6 +89,7 @@ struct BwdArgs {
     void* gx;  // may be nullptr
     float* gx_part;  // [osplit][B][I] float scratch, used when cfg.osplit > 1
     float* partials;
+    float* colpart;  // [grid_b][out_dim] column sums of this tile's grad_y rows (written by the CTAs of column block 0); may be nullptr
 };
 
 // Backward of the base term (qk_base.cu): runs after the circuit backward, adds its part to grad_x in place.
@@ -103,13 +104,34 @@ struct BaseBwdArgs {
 };
 
 FwdCfg choose_fwd_cfg(const QkDesc& d, bool edges, bool base, bool xtrig);
+
+// Developer overrides (qk_debug_set in the C ABI; first use also reads the QK_* environment variables once).
+enum DebugKey { kDbgBwdGroups = 0, kDbgBwdRpg, kDbgBwdRu, kDbgBwdOsplit, kDbgNoXtrig, kDbgVerbose, kDbgCount };
+int debug_get(int key);
+void debug_set(int key, int value);
+
+// Largest dynamic shared memory any tile chooser hands out; each kernel instantiation is opted in to it once per device.
+constexpr int kSmemCap = 200 * 1024;
+// Opts `kern` in to kSmemCap bytes of dynamic shared memory on the current device, once: `mask` is that
+// instantiation's own set of devices already done. The attribute is set before the bit, so a second host thread
+// either sees the bit (attribute in place) or sets the same value again. A cudaDeviceReset() forgets the attribute
+// but not the bit: a process that resets a device must not call the library on it afterwards.
+template <typename K>
+inline cudaError_t opt_in_smem(K kern, unsigned long long* mask) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    const unsigned long long bit = 1ull << (dev & 63);
+    if (__atomic_load_n(mask, __ATOMIC_ACQUIRE) & bit) return cudaSuccess;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemCap);
+    if (e == cudaSuccess) __atomic_fetch_or(mask, bit, __ATOMIC_RELEASE);
+    return e;
+}
 BwdCfg choose_bwd_cfg(const QkDesc& d);
 int base_rows_per_cta(int batch, int in_dim);
 cudaError_t launch_base_backward(const BaseBwdArgs& a, int io_dtype, cudaStream_t st);
 
 cudaError_t launch_prep(const PrepArgs& a, cudaStream_t st);
-cudaError_t launch_colsum(const void* gy, int io_dtype, int B, int O, int nsplit, float* part,
-                          cudaStream_t st);
 cudaError_t launch_finish(const FinishArgs& a, cudaStream_t st);
 // gx[n] = sum over the output slices of part[s][n], in slice order, stored in the I/O dtype
 cudaError_t launch_sum_gx(const float* part, void* gx, int io_dtype, size_t n, int nslices, cudaStream_t st);

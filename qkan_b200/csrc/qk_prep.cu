@@ -1,21 +1,24 @@
 // Small set-up and finishing kernels around the two hot kernels:
-//   prep_table   : per-edge constant table (trig of theta, merged phases, folded mask)
-//   prep_bias    : bias[o] = sum_i postact_bias * postact_weights * mask
-//   colsum       : column sums of grad_y (needed by the postact_bias terms)
+//   prep         : per-edge constant table(s) (trig of theta, merged phases, folded mask) and
+//                  bias[o] = sum_i postact_bias * postact_weights * mask, one launch
 //   finish_grads : fixed-order sum of the per-batch-tile partials into the
 //                  reference's parameter layouts
+// (the column sums of grad_y that the postact-bias terms need are taken inside the backward kernel)
 #include "qk_kernels.cuh"
 
 namespace qk {
 
-__global__ void prep_table_kernel(PrepArgs a) {
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    const int o = blockIdx.y;
-    if (i >= a.ipad) return;
+// Constants of edge (o, i) into the generic table and, when wanted, into the frozen-preact forward's table
+// (same layout; its rows (pw_l, c_l) hold (cos c_l, sin c_l)).
+__device__ void prep_edge(const PrepArgs& a, int o, int i) {
     const int R = a.reps, RK = a.rk;
     const int K = table_stride(RK);
     float* t = a.table + ((size_t)o * a.ipad + i) * K;
-    auto put = [&](int row, float v) { t[row] = v; };
+    float* tx = a.table_x ? a.table_x + ((size_t)o * a.ipad + i) * K : nullptr;
+    auto put = [&](int row, float v) {
+        t[row] = v;
+        if (tx) tx[row] = v;
+    };
     if (i >= a.in_dim) {
         for (int k = 0; k < K; ++k) put(k, 0.f);
         return;
@@ -60,14 +63,15 @@ __global__ void prep_table_kernel(PrepArgs a) {
     put(t_ca0(RK), ca0);
     put(t_sa0(RK), sa0);
     for (int l = 0; l < RK; ++l) {
-        if (l < R && a.xtrig) {  // frozen preacts, angle x + c_l: the forward wants cos/sin of c_l
-            float s, c;
-            sincosf(th_rz(l + 1), &s, &c);
-            put(t_pw(l), c);
-            put(t_c(l), s);
-        } else if (l < R) {
+        if (l < R) {
             put(t_pw(l), ptr ? a.pw[q * R + l] : 1.f);
             put(t_c(l), (ptr ? a.pb[q * R + l] : 0.f) + th_rz(l + 1));
+            if (tx) {  // frozen preacts, angle x + c_l: that forward wants cos/sin of c_l
+                float s, c;
+                sincosf(th_rz(l + 1), &s, &c);
+                tx[t_pw(l)] = c;
+                tx[t_c(l)] = s;
+            }
         } else {  // identity padding
             put(t_pw(l), 0.f);
             put(t_c(l), 0.f);
@@ -87,58 +91,46 @@ __global__ void prep_table_kernel(PrepArgs a) {
     put(t_bw(RK), bw);
 }
 
-// one warp per output: fixed lane-strided order + shuffle tree => deterministic
-__global__ void prep_bias_kernel(PrepArgs a) {
-    const int o = blockIdx.x * (blockDim.x / kWarp) + threadIdx.x / kWarp;
-    const int lane = threadIdx.x % kWarp;
-    if (o >= a.out_dim) return;
+// One CTA per output: its threads walk the input columns, write each edge's constants and add up
+// bias[o] = sum_i postact_bias * postact_weights * mask in a fixed order (thread-strided partial sums, then a
+// shared-memory tree): run-to-run reproducible.
+constexpr int kPrepThreads = 128;
+__global__ void __launch_bounds__(kPrepThreads) prep_kernel(PrepArgs a) {
+    __shared__ float sm[kPrepThreads];
+    const int o = blockIdx.x;
+    const bool want_bias = a.bias != nullptr;
+    const bool use_pb = want_bias && a.postb && (a.flags & QK_USE_POSTACT_BIAS);
     float s = 0.f;
-    if (a.postb && (a.flags & QK_USE_POSTACT_BIAS)) {
-        for (int i = lane; i < a.in_dim; i += kWarp) {
-            size_t e = (size_t)o * a.in_dim + i;
-            float m = a.mask ? ld_param(a.mask, a.param_dtype, e) : 1.f;
-            float w = a.postw ? ld_param(a.postw, a.param_dtype, e) * m : 1.f;
+    for (int i = threadIdx.x; i < a.ipad; i += kPrepThreads) {
+        prep_edge(a, o, i);
+        if (use_pb && i < a.in_dim) {
+            const size_t e = (size_t)o * a.in_dim + i;
+            const float m = a.mask ? ld_param(a.mask, a.param_dtype, e) : 1.f;
+            const float w = a.postw ? ld_param(a.postw, a.param_dtype, e) * m : 1.f;
             s = fmaf(ld_param(a.postb, a.param_dtype, e), w, s);
         }
     }
-#pragma unroll
-    for (int d = 16; d >= 1; d >>= 1) s += __shfl_xor_sync(0xffffffffu, s, d);
-    if (lane == 0) a.bias[o] = s;
-}
-
-// partial column sums: grid (ceil(O/32), nsplit); block (32, 8)
-template <typename IO>
-__global__ void colsum_kernel(const IO* __restrict__ gy, int B, int O, int nsplit,
-                              float* __restrict__ part) {
-    __shared__ float sm[8][kWarp];
-    const int o = blockIdx.x * kWarp + threadIdx.x;
-    const int split = blockIdx.y;
-    const int rows_per = (B + nsplit - 1) / nsplit;
-    const int r0 = split * rows_per;
-    const int r1 = min(B, r0 + rows_per);
-    float s = 0.f;
-    if (o < O)
-        for (int r = r0 + threadIdx.y; r < r1; r += 8) s += ld_as_float(gy + (size_t)r * O + o);
-    sm[threadIdx.y][threadIdx.x] = s;
+    if (!want_bias) return;
+    sm[threadIdx.x] = s;
     __syncthreads();
-    if (threadIdx.y == 0 && o < O) {
-        float t = 0.f;
-#pragma unroll
-        for (int k = 0; k < 8; ++k) t += sm[k][threadIdx.x];
-        part[(size_t)split * O + o] = t;
+    for (int d = kPrepThreads / 2; d >= 1; d >>= 1) {
+        if (threadIdx.x < d) sm[threadIdx.x] += sm[threadIdx.x + d];
+        __syncthreads();
     }
+    if (threadIdx.x == 0) a.bias[o] = sm[0];
 }
 
 // Block = 32 input columns (one lane each) x `blockDim.y` tile slices. Every slice adds the per-tile
 // partials t = slice, slice + slices, ... of each accumulator row; slice 0 then adds the slice sums in
 // order and writes the gradients. Fixed order throughout: run-to-run bitwise reproducible.
 __global__ void finish_grads_kernel(FinishArgs a) {
-    extern __shared__ float part[];  // [slices][nacc + 1][32]; the extra row is the base-term kernel's partials
+    // [slices][nacc + 2][32]; the extra rows are the base-term kernel's partials and the column sums of grad_y
+    extern __shared__ float part[];
     const int lane = threadIdx.x, slice = threadIdx.y, slices = blockDim.y;
     const int i = blockIdx.x * kWarp + lane;  // < ipad
     const int o = blockIdx.y;
     const int R = a.reps, RK = a.rk;
-    const int nacc = a.nacc, nrow = a.nacc + 1;
+    const int nacc = a.nacc, nrow = a.nacc + 2;
     const size_t tile_stride = (size_t)a.out_dim * nacc * a.ipad;
     const float* p0 = a.partials + ((size_t)o * nacc) * a.ipad + i;
     for (int k = 0; k < nacc; ++k) {
@@ -154,6 +146,13 @@ __global__ void finish_grads_kernel(FinishArgs a) {
             for (int t = slice; t < a.base_tiles; t += slices) s += bp[(size_t)t * a.out_dim * a.ipad];
         }
         part[(slice * nrow + nacc) * kWarp + lane] = s;
+    }
+    {
+        // sum_b grad_y[b,o] from the per-tile column sums (the same value in every lane)
+        float s = 0.f;
+        if (a.colpart)
+            for (int t = slice; t < a.ntiles; t += slices) s += a.colpart[(size_t)t * a.out_dim + o];
+        part[(slice * nrow + nacc + 1) * kWarp + lane] = s;
     }
     __syncthreads();
     if (slice != 0 || i >= a.in_dim) return;
@@ -198,9 +197,7 @@ __global__ void finish_grads_kernel(FinishArgs a) {
             for (int l = 0; l < R; ++l) a.gpw[e * R + l] = ptr ? total(a_pwx(RK, l)) : 0.f;
     }
     if (a.gpostw || a.gpostb || a.gbasew) {
-        float cs = 0.f;
-        if (use_pb && a.colsum)
-            for (int s = 0; s < a.ncolsplit; ++s) cs += a.colsum[(size_t)s * a.out_dim + o];
+        const float cs = (use_pb && a.colpart) ? total(nacc + 1) : 0.f;
         float m = a.mask ? ld_param(a.mask, a.param_dtype, e) : 1.f;
         if (a.gpostw) {
             float pbv = use_pb ? ld_param(a.postb, a.param_dtype, e) : 0.f;
@@ -262,19 +259,7 @@ cudaError_t launch_sum_gx(const float* part, void* gx, int io_dtype, size_t n, i
 }
 
 cudaError_t launch_prep(const PrepArgs& a, cudaStream_t st) {
-    dim3 grid((a.ipad + 127) / 128, a.out_dim);
-    prep_table_kernel<<<grid, 128, 0, st>>>(a);
-    if (a.bias) prep_bias_kernel<<<(a.out_dim + 3) / 4, 128, 0, st>>>(a);
-    return cudaPeekAtLastError();
-}
-
-cudaError_t launch_colsum(const void* gy, int io_dtype, int B, int O, int nsplit, float* part,
-                          cudaStream_t st) {
-    dim3 grid((O + kWarp - 1) / kWarp, nsplit), block(kWarp, 8);
-    if (io_dtype == QK_BF16)
-        colsum_kernel<<<grid, block, 0, st>>>(static_cast<const __nv_bfloat16*>(gy), B, O, nsplit, part);
-    else
-        colsum_kernel<<<grid, block, 0, st>>>(static_cast<const float*>(gy), B, O, nsplit, part);
+    prep_kernel<<<a.out_dim, kPrepThreads, 0, st>>>(a);
     return cudaPeekAtLastError();
 }
 
@@ -282,10 +267,10 @@ cudaError_t launch_finish(const FinishArgs& a, cudaStream_t st) {
     // as many tile slices as there are tiles to share out, within 48 KB of shared memory
     int slices = 8;
     const int most_tiles = a.ntiles > a.base_tiles ? a.ntiles : a.base_tiles;
-    while (slices > 1 && (slices / 2 >= most_tiles || (size_t)slices * (a.nacc + 1) * kWarp * sizeof(float) > 48 * 1024))
+    while (slices > 1 && (slices / 2 >= most_tiles || (size_t)slices * (a.nacc + 2) * kWarp * sizeof(float) > 48 * 1024))
         slices /= 2;
     dim3 grid(a.ipad / kWarp, a.out_dim), block(kWarp, slices);
-    finish_grads_kernel<<<grid, block, (size_t)slices * (a.nacc + 1) * kWarp * sizeof(float), st>>>(a);
+    finish_grads_kernel<<<grid, block, (size_t)slices * (a.nacc + 2) * kWarp * sizeof(float), st>>>(a);
     return cudaPeekAtLastError();
 }
 

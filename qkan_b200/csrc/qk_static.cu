@@ -42,9 +42,13 @@ int qk_pz_forward_noalloc(const QkDesc* desc, const void* x, const float* theta,
                           const void* base_weight, const void* mask, void* y, void* cuda_stream) {
     g_static_err[0] = 0;
     const size_t need = qk_forward_workspace_bytes(desc);
-    if (need == 0) {  // the descriptor itself was rejected; qk_last_error() has the reason
-        snprintf(g_static_err, sizeof(g_static_err), "invalid descriptor: %s", qk_last_error());
-        return QK_ERR_BAD_ARGUMENT;
+    if (need == 0) {
+        // the descriptor itself was rejected: let the regular entry point name the reason, so that both entry
+        // points answer a bad or unsupported descriptor with the same code (it fails before touching memory)
+        const int rc = qk_pz_forward(desc, x, theta, preacts_weight, preacts_bias, postact_weights,
+                                     postact_bias, base_weight, mask, y, nullptr, 0, cuda_stream);
+        snprintf(g_static_err, sizeof(g_static_err), "%s", qk_last_error());
+        return rc != QK_OK ? rc : QK_ERR_BAD_ARGUMENT;
     }
     if (need > kStaticScratchBytes) {
         snprintf(g_static_err, sizeof(g_static_err),

@@ -13,22 +13,19 @@ import torch
 
 from . import _abi
 
-_WORKSPACES: dict = {}
-
 
 def _ptr(t: Optional[torch.Tensor]):
     return None if t is None else t.data_ptr()
 
 
 def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
-    """Scratch owned by the caller side of the ABI: one growing buffer per (device, stream)."""
-    stream = torch.cuda.current_stream(device)
-    key = (device.index, stream.cuda_stream)
-    buf = _WORKSPACES.get(key)
-    if buf is None or buf.numel() < nbytes:
-        buf = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=device)
-        _WORKSPACES[key] = buf
-    return buf
+    """Scratch owned by the caller side of the ABI: a fresh block from torch's caching allocator per call.
+
+    The allocator hands the same cached block back call after call (no ``cudaMalloc`` once warm), keeps blocks
+    apart per stream, and inside a CUDA-graph capture takes them from the graph's private pool, so a captured
+    address can never be handed to anyone else. 512-byte alignment is the allocator's own.
+    """
+    return torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=device)
 
 
 def _io_dtype(t: torch.Tensor) -> int:
@@ -117,11 +114,125 @@ def _preact_shape(desc: _abi.QkDesc):
     return (desc.group, desc.reps) if desc.group else (desc.out_dim, desc.in_dim, desc.reps)
 
 
+class PreparedLayer:
+    """Per-edge constants of one layer for unchanged parameters: the output of ``qk_pz_prepare``.
+
+    ``tables`` is the device buffer the ``*_prepared`` entry points read; ``postw`` / ``postb`` / ``mask`` are the
+    converted (O,I) tensors the backward's finishing kernel reads again. The state has no batch axis: it serves
+    any number of rows, float32 or bfloat16 activations, until a parameter value changes.
+    """
+
+    __slots__ = ("tables", "postw", "postb", "mask", "has_base", "shape", "reps", "flags", "param_dtype",
+                 "ansatz_code", "group", "theta_shape")
+
+    def desc(self, x: torch.Tensor) -> _abi.QkDesc:
+        if x.dim() != 2 or x.shape[1] != self.shape[1]:
+            raise ValueError(f"x {tuple(x.shape)} does not match the prepared layer ({self.shape[1]} inputs)")
+        return _abi.QkDesc(x.shape[0], self.shape[1], self.shape[0], self.reps, _io_dtype(x), self.param_dtype,
+                           self.flags, self.ansatz_code, self.group)
+
+
+def prepare_layer(theta, pw, pb, postw, postb=None, basew=None, mask=None, *, in_dim: int,
+                  preact_trainable: bool, fast_measure: bool = True, use_postact_bias: bool = False,
+                  ansatz: str = "pz_encoding", precise: bool = False) -> PreparedLayer:
+    """Run the set-up kernel once (``qk_pz_prepare``): tables and folded bias for these parameter values."""
+    lib = _abi.load()
+    _require_cuda(theta, "theta")
+    dev = theta.device
+    theta, pw, pb = _f32c(theta), _f32c(pw), _f32c(pb)
+    postw, postb, basew, mask, pdt = _oi_params(postw, postb if use_postact_bias else None, basew, mask)
+    flags = _flags(preact_trainable, fast_measure, use_postact_bias and postb is not None, precise)
+    probe = torch.empty((0, in_dim), dtype=torch.float32, device="meta")
+    d = _make_desc(probe, theta, flags, pdt, ansatz, out_dim=postw.shape[0])
+    prep = PreparedLayer()
+    prep.postw, prep.postb, prep.mask, prep.has_base = postw, postb, mask, basew is not None
+    prep.shape, prep.reps, prep.flags, prep.param_dtype = (d.out_dim, d.in_dim), d.reps, flags, pdt
+    prep.ansatz_code, prep.group, prep.theta_shape = d.ansatz, d.group, tuple(theta.shape)
+    with torch.cuda.device(dev):
+        nbytes = lib.qk_tables_bytes(_abi.desc_pointer(d))
+        _abi.check(0 if nbytes else _abi.QK_ERR_BAD_ARGUMENT, "qk_tables_bytes")
+        prep.tables = _workspace(dev, nbytes)
+        rc = lib.qk_pz_prepare(_abi.desc_pointer(d), _ptr(theta), _ptr(pw), _ptr(pb), _ptr(postw), _ptr(postb),
+                               _ptr(basew), _ptr(mask), _ptr(prep.tables), prep.tables.numel(),
+                               torch.cuda.current_stream(dev).cuda_stream)
+    _abi.check(rc, "qk_pz_prepare")
+    return prep
+
+
+def _check_out(t, shape, dtype, dev, name):
+    if (tuple(t.shape) != tuple(shape) and t.numel() != torch.Size(shape).numel()) or t.dtype != dtype \
+            or t.device != dev or not t.is_contiguous():
+        raise ValueError(f"{name} must be a contiguous {dtype} tensor of {tuple(shape)} on {dev}")
+
+
+def forward_prepared(prep: PreparedLayer, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``y (B,O)`` from prepared tables: one launch (``qk_pz_forward_prepared``)."""
+    lib = _abi.load()
+    _require_cuda(x, "x")
+    x = x.detach().contiguous()
+    desc = prep.desc(x)
+    if out is None:
+        y = torch.empty((x.shape[0], desc.out_dim), dtype=x.dtype, device=x.device)
+    else:
+        y = out
+        if tuple(y.shape) != (x.shape[0], desc.out_dim):
+            raise ValueError(f"out must be a contiguous {x.dtype} tensor of {(x.shape[0], desc.out_dim)} on {x.device}")
+        _check_out(y, (x.shape[0], desc.out_dim), x.dtype, x.device, "out")
+    with torch.cuda.device(x.device):
+        rc = lib.qk_pz_forward_prepared(_abi.desc_pointer(desc), _ptr(x), _ptr(prep.tables), prep.tables.numel(),
+                                        int(prep.has_base), _ptr(y), torch.cuda.current_stream(x.device).cuda_stream)
+    _abi.check(rc, "qk_pz_forward_prepared")
+    return y
+
+
+_GRAD_NAMES = ("x", "theta", "preacts_weight", "preacts_bias", "postact_weights", "postact_bias", "base_weight")
+
+
+def backward_prepared(prep: PreparedLayer, x: torch.Tensor, gy: torch.Tensor, *, want=_GRAD_NAMES,
+                      out: Optional[dict] = None) -> dict:
+    """Gradients from prepared tables: backward + finish launches (``qk_pz_backward_prepared``)."""
+    lib = _abi.load()
+    _require_cuda(x, "x")
+    x = x.detach().contiguous()
+    gy = gy.detach().to(x.dtype).contiguous()
+    desc = prep.desc(x)
+    O, I = desc.out_dim, desc.in_dim
+    dev = x.device
+    shapes = {"x": tuple(x.shape), "theta": prep.theta_shape, "preacts_weight": _preact_shape(desc),
+              "preacts_bias": _preact_shape(desc), "postact_weights": (O, I), "postact_bias": (O, I),
+              "base_weight": (O, I)}
+    given = out or {}
+    out = {}
+    for name in want:
+        dt = x.dtype if name == "x" else torch.float32
+        t = given.get(name)
+        if t is None:
+            t = torch.empty(shapes[name], dtype=dt, device=dev)
+        else:
+            _check_out(t, shapes[name], dt, dev, f"out[{name!r}]")
+        out[name] = t
+    with torch.cuda.device(dev):
+        nbytes = lib.qk_backward_scratch_bytes(_abi.desc_pointer(desc))
+        ws = _workspace(dev, nbytes)
+        rc = lib.qk_pz_backward_prepared(
+            _abi.desc_pointer(desc), _ptr(x), _ptr(prep.tables), prep.tables.numel(), _ptr(prep.postw),
+            _ptr(prep.postb), _ptr(prep.mask), int(prep.has_base), _ptr(gy), _ptr(out.get("x")),
+            _ptr(out.get("theta")), _ptr(out.get("preacts_weight")), _ptr(out.get("preacts_bias")),
+            _ptr(out.get("postact_weights")), _ptr(out.get("postact_bias")), _ptr(out.get("base_weight")),
+            _ptr(ws), ws.numel(), torch.cuda.current_stream(dev).cuda_stream)
+    _abi.check(rc, "qk_pz_backward_prepared")
+    return out
+
+
 def layer_forward(x, theta, pw, pb, postw, postb=None, basew=None, mask=None, *,
                   preact_trainable: bool, fast_measure: bool = True,
                   use_postact_bias: bool = False, ansatz: str = "pz_encoding",
                   precise: bool = False, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """``y (B,O)`` of the fused layer; no autograd (see ``qkan_layer``). ``out``: preallocated contiguous result."""
+    """``y (B,O)`` of the fused layer; no autograd (see ``qkan_layer``). ``out``: preallocated contiguous result.
+
+    Set-up and forward in one C-ABI call (``qk_pz_forward``); with unchanged parameters use ``prepare_layer`` once
+    and ``forward_prepared`` / ``backward_prepared`` after it.
+    """
     lib = _abi.load()
     _require_cuda(x, "x")
     x = x.detach().contiguous()
@@ -148,8 +259,7 @@ def layer_forward(x, theta, pw, pb, postw, postb=None, basew=None, mask=None, *,
 
 def layer_backward(x, theta, pw, pb, postw, postb, basew, mask, gy, *, preact_trainable: bool,
                    fast_measure: bool = True, use_postact_bias: bool = False,
-                   want=("x", "theta", "preacts_weight", "preacts_bias", "postact_weights",
-                         "postact_bias", "base_weight"), out: Optional[dict] = None,
+                   want=_GRAD_NAMES, out: Optional[dict] = None,
                    ansatz: str = "pz_encoding", precise: bool = False) -> dict:
     """Gradients of ``sum(y * gy)`` named as the reference's parameters; float32 except ``x``.
 
@@ -253,37 +363,37 @@ def _uses_preacts(preact_trainable: bool, ansatz: str) -> bool:
 
 
 class _LayerFunction(torch.autograd.Function):
+    """Forward: set-up + forward kernel; the prepared tables are kept for the backward (two more launches)."""
+
     @staticmethod
     def forward(ctx, x, theta, pw, pb, postw, postb, basew, mask, preact_trainable, fast_measure,
                 use_postact_bias, ansatz, precise):
-        # theta / preacts reach the kernels as float32; converted once here and kept for the backward
-        theta32, pw32, pb32 = _f32c(theta), _f32c(pw), _f32c(pb)
-        ctx.save_for_backward(x, theta32, pw32, pb32, postw, postb, basew, mask)
-        ctx.cfg = (preact_trainable, fast_measure, use_postact_bias, ansatz, precise)
-        ctx.meta = [(t.dtype, t.shape) if t is not None else None for t in (x, theta, pw, pb, postw, postb, basew)]
-        return layer_forward(x, theta32, pw32, pb32, postw, postb, basew, mask,
+        prep = prepare_layer(theta, pw, pb, postw, postb, basew, mask, in_dim=x.shape[1],
                              preact_trainable=preact_trainable, fast_measure=fast_measure,
                              use_postact_bias=use_postact_bias, ansatz=ansatz, precise=precise)
+        y = forward_prepared(prep, x)
+        ctx.save_for_backward(x)
+        ctx.prep = prep
+        ctx.cfg = (preact_trainable, use_postact_bias, ansatz)
+        ctx.meta = [(t.dtype, t.shape) if t is not None else None for t in (x, theta, pw, pb, postw, postb, basew)]
+        return y
 
     @staticmethod
     def backward(ctx, gy):
-        x, theta, pw, pb, postw, postb, basew, mask = ctx.saved_tensors
-        preact_trainable, fast_measure, use_postact_bias, ansatz, precise = ctx.cfg
-        names = ("x", "theta", "preacts_weight", "preacts_bias", "postact_weights", "postact_bias",
-                 "base_weight")
+        (x,) = ctx.saved_tensors
+        prep = ctx.prep
+        preact_trainable, use_postact_bias, ansatz = ctx.cfg
         need = ctx.needs_input_grad
-        want = tuple(n for k, n in enumerate(names) if need[k])
+        want = tuple(n for k, n in enumerate(_GRAD_NAMES) if need[k])
         if not _uses_preacts(preact_trainable, ansatz):
             want = tuple(n for n in want if n not in ("preacts_weight", "preacts_bias"))
-        if postb is None or not use_postact_bias:
+        if prep.postb is None or not use_postact_bias:
             want = tuple(n for n in want if n != "postact_bias")
-        if basew is None:
+        if not prep.has_base:
             want = tuple(n for n in want if n != "base_weight")
-        g = layer_backward(x, theta, pw, pb, postw, postb, basew, mask, gy,
-                           preact_trainable=preact_trainable, fast_measure=fast_measure,
-                           use_postact_bias=use_postact_bias, want=want, ansatz=ansatz, precise=precise)
+        g = backward_prepared(prep, x, gy, want=want)
         outs = []
-        for k, n in enumerate(names):
+        for k, n in enumerate(_GRAD_NAMES):
             t = g.get(n)
             if t is not None and ctx.meta[k] is not None:
                 dtype, shape = ctx.meta[k]

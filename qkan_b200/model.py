@@ -236,11 +236,13 @@ class QKAN(nn.Module):
         Same signature, defaults and return value as the reference (``src/qkan/qkan.py:1658-1893``):
         Adam(lr=5e-4) and MSE unless given, LBFGS gets the built-in closure, the result is
         ``{"train_loss": [...], "test_loss": [...], "reg": [...]}`` with one entry per step.
-        Under ``torch.distributed`` the gradients are averaged over the ranks after each backward.
+        Under ``torch.distributed`` the gradients are averaged over the ranks after each backward, and the
+        objective a closure returns, the logged losses and the value the scheduler sees are means over the ranks,
+        so that every rank's optimiser and scheduler take the same decisions (LBFGS line searches included).
         """
         from tqdm import tqdm
 
-        from .parallel import sync_module_grads
+        from .parallel import mean_over_ranks, sync_module_grads
 
         if lamb > 0.0 and not self.save_act:
             lamb = 0.0
@@ -273,8 +275,10 @@ class QKAN(nn.Module):
             sync_module_grads(self)
             if clip_theta_grad_norm is not None and theta_params:
                 torch.nn.utils.clip_grad_norm_(theta_params, max_norm=clip_theta_grad_norm)
-            state["train_loss"], state["reg"] = train_loss, reg
-            return objective
+            # Every rank hands its optimiser the same objective (the mean over the row shards, matching the
+            # averaged gradients): closure-driven optimisers choose their next collective from this value.
+            state["train_loss"], state["reg"] = mean_over_ranks(train_loss), mean_over_ranks(reg)
+            return mean_over_ranks(objective)
 
         def default_closure():
             optimizer.zero_grad()
@@ -311,6 +315,7 @@ class QKAN(nn.Module):
             with torch.no_grad():
                 test_loss = loss_fn(self.forward(dataset["test_input"][test_id].to(self.device)),
                                     dataset["test_label"][test_id].to(self.device))
+            test_loss = mean_over_ranks(test_loss)  # one value for every rank's scheduler
             if scheduler is not None:
                 scheduler.step(test_loss)
             train_loss = state["train_loss"]

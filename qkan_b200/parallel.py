@@ -122,6 +122,20 @@ def layer_grad_shapes(in_dim: int, out_dim: int, reps: int, *, preact_trainable:
     return shapes
 
 
+def mean_over_ranks(value: torch.Tensor, group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
+    """The mean of a scalar over the ranks (detached); the value itself without an initialised process group.
+
+    A training loop must hand its optimiser and its scheduler the SAME number on every rank: LBFGS decides from
+    the loss how many more closure calls (each one a collective) to make, and a plateau scheduler decides from
+    it when to cut the learning rate. Per-rank losses would let the ranks drift apart, or deadlock.
+    """
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size(group) == 1:
+        return value
+    out = value.detach().clone().to(torch.float32)
+    dist.all_reduce(out, op=dist.ReduceOp.SUM, group=group)
+    return (out / dist.get_world_size(group)).to(value.dtype)
+
+
 def sync_module_grads(module: torch.nn.Module, group: Optional[dist.ProcessGroup] = None,
                       average: bool = True) -> int:
     """All-reduce every ``.grad`` of ``module`` through one flat buffer; returns the bytes moved.
@@ -145,3 +159,94 @@ def sync_module_grads(module: torch.nn.Module, group: Optional[dist.ProcessGroup
         g.copy_(flat[off: off + n].view_as(g))
         off += n
     return flat.numel() * 4
+
+
+class OverlappedGradSync:
+    """Data-parallel gradient averaging for a multi-layer model, one collective per layer, overlapped with backward.
+
+    The parameters are grouped layer by layer (``groups``: by default each direct child of ``module.layers``, or
+    of ``module`` itself). Each group's ``.grad`` tensors are views of one flat float32 buffer. Autograd
+    accumulates into the views; a post-accumulate hook counts the group's parameters as they become ready, and
+    when the last one is, the group's buffer is all-reduced asynchronously on the collective stream while autograd
+    goes on with the layers nearer the input. ``finish()`` waits for the collectives and applies the 1/world
+    average. The reference has no counterpart (it leaves data parallelism to the user, ``src/qkan/info.py:62-75``);
+    the rows of a batch are independent, so this sum is the only exchange of a training step.
+
+    Usage per step: ``sync.zero_grad(); loss.backward(); sync.finish(); optimizer.step()``. Do not call
+    ``optimizer.zero_grad(set_to_none=True)`` in between: it would detach the views (``zero_grad()`` here
+    re-attaches them).
+    """
+
+    def __init__(self, module: torch.nn.Module, groups: Optional[list] = None,
+                 group: Optional[dist.ProcessGroup] = None, average: bool = True):
+        if groups is None:
+            children = list(getattr(module, "layers", module).children()) or [module]
+            groups = [[p for p in c.parameters() if p.requires_grad] for c in children]
+            seen = {id(p) for g in groups for p in g}
+            rest = [p for p in module.parameters() if p.requires_grad and id(p) not in seen]
+            if rest:
+                groups.append(rest)
+        self.groups = [g for g in groups if g]
+        self.pg, self.average = group, average
+        self.flats, self._pending, self._handles, self._hooks = [], [], [], []
+        for gi, params in enumerate(self.groups):
+            dev = params[0].device
+            n = sum((p.numel() + 63) // 64 * 64 for p in params)
+            flat = torch.zeros(n, dtype=torch.float32, device=dev)
+            self.flats.append(flat)
+            self._pending.append(0)
+            for p in params:
+                if p.dtype != torch.float32:
+                    raise TypeError("OverlappedGradSync buckets float32 parameters; keep low-precision copies outside")
+                self._hooks.append(p.register_post_accumulate_grad_hook(self._make_hook(gi)))
+        self._attach()
+
+    def _attach(self) -> None:
+        for flat, params in zip(self.flats, self.groups):
+            off = 0
+            for p in params:
+                p.grad = flat[off: off + p.numel()].view_as(p)
+                off += (p.numel() + 63) // 64 * 64
+
+    def _make_hook(self, gi: int):
+        def hook(_param):
+            self._pending[gi] -= 1
+            if self._pending[gi] == 0:
+                self._launch(gi)
+        return hook
+
+    def _launch(self, gi: int) -> None:
+        if dist.is_available() and dist.is_initialized() and dist.get_world_size(self.pg) > 1:
+            self._handles.append(dist.all_reduce(self.flats[gi], op=dist.ReduceOp.SUM, group=self.pg, async_op=True))
+
+    def zero_grad(self) -> None:
+        """Clear the buckets, re-attach the views and arm the ready counters for the next backward."""
+        for gi, flat in enumerate(self.flats):
+            flat.zero_()
+            self._pending[gi] = len(self.groups[gi])
+        self._handles = []
+        self._attach()
+
+    def finish(self) -> None:
+        """Wait for the collectives of this backward (groups whose hooks never fired, because a parameter
+        got no gradient, are reduced here) and turn the sums into means."""
+        for gi, left in enumerate(self._pending):
+            if left > 0:
+                self._pending[gi] = 0
+                self._launch(gi)
+        for h in self._handles:
+            h.wait()
+        self._handles = []
+        if self.average and dist.is_available() and dist.is_initialized():
+            world = dist.get_world_size(self.pg)
+            if world > 1:
+                for flat in self.flats:
+                    flat.div_(world)
+
+    def nbytes(self) -> int:
+        return sum(f.numel() * 4 for f in self.flats)
+
+    def remove(self) -> None:
+        for h in self._hooks:
+            h.remove()
+        self._hooks = []

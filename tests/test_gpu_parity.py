@@ -238,7 +238,7 @@ def test_accuracy_for_large_input_magnitudes(x_scale, precise):
 
 
 @pytest.mark.parametrize("io_dtype,precise", [(torch.float32, False), (torch.float32, True), (torch.bfloat16, False)])
-def test_backward_with_sliced_outputs_matches_oracle(monkeypatch, io_dtype, precise):
+def test_backward_with_sliced_outputs_matches_oracle(io_dtype, precise):
     """Small batches cut the outputs into slices over grid.z and add the grad_x shares afterwards; forced here
     (4 slices of 16, the last one ragged) and compared with the default choice and the oracle."""
     from qkan_b200 import functional as F
@@ -251,15 +251,21 @@ def test_backward_with_sliced_outputs_matches_oracle(monkeypatch, io_dtype, prec
             p[k] = torch.as_tensor(p[k]).to(torch.bfloat16).float().numpy()
     y_ref, g_ref = _run_oracle(p, cfg)
     tol = TOL_F32 if io_dtype == torch.float32 else TOL_BF16
-    monkeypatch.setenv("QK_BWD_OSPLIT", "4")
-    y, g = _run_cuda(p, cfg, io_dtype=io_dtype, precise=precise)
-    _check(y, g, y_ref, g_ref, tol, "sliced")
-    # solver-contract backward (grad_postacts input) through the same slices
-    x, th, pw, pb = (_dev(p[k]) for k in ("x", "theta", "pw", "pb"))
-    gpa = torch.randn(B, O, I, device="cuda")
-    gs = F.postacts_backward(x, th, pw, pb, gpa, preact_trainable=True, precise=precise)
-    monkeypatch.setenv("QK_BWD_OSPLIT", "1")
-    g1 = F.postacts_backward(x, th, pw, pb, gpa, preact_trainable=True, precise=precise)
+    from qkan_b200 import _abi
+
+    lib = _abi.load()
+    try:
+        lib.qk_debug_set(_abi.QK_DBG_BWD_OSPLIT, 4)
+        y, g = _run_cuda(p, cfg, io_dtype=io_dtype, precise=precise)
+        _check(y, g, y_ref, g_ref, tol, "sliced")
+        # solver-contract backward (grad_postacts input) through the same slices
+        x, th, pw, pb = (_dev(p[k]) for k in ("x", "theta", "pw", "pb"))
+        gpa = torch.randn(B, O, I, device="cuda")
+        gs = F.postacts_backward(x, th, pw, pb, gpa, preact_trainable=True, precise=precise)
+        lib.qk_debug_set(_abi.QK_DBG_BWD_OSPLIT, 1)
+        g1 = F.postacts_backward(x, th, pw, pb, gpa, preact_trainable=True, precise=precise)
+    finally:
+        lib.qk_debug_set(_abi.QK_DBG_BWD_OSPLIT, 0)
     for k in g1:
         assert nerr(gs[k].cpu().numpy(), g1[k].cpu().numpy()) <= 2e-6, k
 
@@ -329,3 +335,66 @@ def test_grouped_parameters_with_empty_batch_and_bf16():
     for k in ("theta", "preacts_weight", "preacts_bias"):
         g_ref[k] = reduce_group(g_ref[k], G)
     _check(y, g, y_ref, g_ref, TOL_BF16, "grouped bf16")
+
+
+@pytest.mark.parametrize("frozen,base,io_dtype", [(False, False, torch.float32), (True, True, torch.float32),
+                                                  (True, False, torch.bfloat16)])
+def test_prepared_entry_points_match_oracle_and_one_call_path(frozen, base, io_dtype):
+    """qk_pz_prepare once, then qk_pz_forward_prepared / qk_pz_backward_prepared for two different batches:
+    the tables have no batch axis. Results equal the one-call entry points bit for bit (same kernels, same
+    tables) and meet the oracle bound; the frozen-preact case carries the second (angle-addition) table."""
+    from qkan_b200 import functional as F
+
+    I, O, R = 70, 40, 3
+    cfg = dict(preact_trainable=not frozen, fast_measure=True, use_postact_bias=True)
+    p = random_problem(31, 150, I, O, R, use_pb=True, base=base, masked=True)
+    names = ("theta", "pw", "pb", "postw", "postb", "basew", "mask")
+    if io_dtype == torch.bfloat16:
+        for k in ("x", "gy"):
+            p[k] = torch.as_tensor(p[k]).to(torch.bfloat16).float().numpy()
+    dev = {k: (None if p[k] is None else _dev(p[k])) for k in names}
+    prep = F.prepare_layer(*(dev[k] for k in names), in_dim=I, **cfg)
+    tol = TOL_F32 if io_dtype == torch.float32 else TOL_BF16
+    for rows in (150, 37):
+        q = dict(p, x=p["x"][:rows], gy=p["gy"][:rows])
+        x, gy = _dev(q["x"]).to(io_dtype), _dev(q["gy"]).to(io_dtype)
+        y = F.forward_prepared(prep, x)
+        g = F.backward_prepared(prep, x, gy)
+        y1 = F.layer_forward(x, *(dev[k] for k in names), **cfg)
+        g1 = F.layer_backward(x, *(dev[k] for k in names), gy, **cfg)
+        assert torch.equal(y, y1)
+        for k in g1:
+            if k in g:
+                assert torch.equal(g[k], g1[k]), k
+        y_ref, g_ref = _run_oracle(q, cfg)
+        gn = {k: v.float().cpu().numpy() for k, v in g.items()}
+        if frozen:
+            gn.pop("preacts_weight", None), gn.pop("preacts_bias", None)
+        if not base:
+            gn.pop("base_weight", None)
+        assert nerr(y.float().cpu().numpy(), y_ref) <= tol
+        for k, v in gn.items():
+            assert nerr(v, g_ref[k]) <= tol, f"rows {rows}: grad {k} {nerr(v, g_ref[k]):.3e}"
+
+
+def test_prepared_entry_points_reject_short_or_misaligned_buffers():
+    from qkan_b200 import _abi
+
+    lib = _abi.load()
+    desc = _abi.QkDesc(8, 4, 3, 2, _abi.QK_F32, _abi.QK_F32, _abi.QK_FAST_MEASURE, _abi.QK_ANSATZ_PZ)
+    dp = _abi.desc_pointer(desc)
+    nt, ns = lib.qk_tables_bytes(dp), lib.qk_backward_scratch_bytes(dp)
+    assert nt > 0 and ns > 0 and lib.qk_backward_workspace_bytes(dp) == nt + ns
+    assert lib.qk_forward_workspace_bytes(dp) == nt  # frozen preacts: generic table + angle-addition table + bias
+    tab = torch.zeros(nt + 512, dtype=torch.uint8, device="cuda")
+    t = torch.zeros(4096, device="cuda")
+    tp = (tab.data_ptr() + 255) // 256 * 256
+    prm = [t.data_ptr()] * 4 + [None, None, None]
+    assert lib.qk_pz_prepare(dp, *prm, tp, nt - 1, None) == _abi.QK_ERR_WORKSPACE
+    assert lib.qk_pz_prepare(dp, *prm, tp + 8, nt, None) == _abi.QK_ERR_WORKSPACE
+    assert lib.qk_pz_prepare(dp, None, *prm[1:], tp, nt, None) == _abi.QK_ERR_BAD_ARGUMENT
+    assert lib.qk_pz_prepare(dp, *prm, tp, nt, None) == _abi.QK_OK
+    assert lib.qk_pz_forward_prepared(dp, t.data_ptr(), tp, nt - 1, 0, t.data_ptr(), None) == _abi.QK_ERR_WORKSPACE
+    assert lib.qk_pz_forward_prepared(dp, t.data_ptr(), tp, nt, 0, None, None) == _abi.QK_ERR_BAD_ARGUMENT
+    assert lib.qk_pz_forward_prepared(dp, t.data_ptr(), tp, nt, 0, t.data_ptr(), None) == _abi.QK_OK
+    torch.cuda.synchronize()
