@@ -151,6 +151,20 @@ int qk_pz_backward_prepared(const QkDesc* desc, const void* x, const void* table
                             void* scratch, size_t scratch_bytes, void* cuda_stream);
 
 /*
+ * Per-edge activation scale: edge_std[o,i] = unbiased standard deviation over the batch of the edge output
+ *   (postacts[b,o,i] + postact_bias[o,i]) * postact_weights[o,i] * mask[o,i] + silu(x[b,i]) * base_weight[o,i] * mask[o,i]
+ * i.e. torch.std(QKANLayer.forward_no_sum(x), dim=0) of the reference (src/qkan/qkan.py:835-891), which its
+ * save_act pass computes for the activation-scale regulariser and pruning (src/qkan/qkan.py:1280-1302). The
+ * (B,O,I) tensor is never formed: per-tile sums of the shifted values and their squares are reduced in a fixed
+ * order. `tables` comes from qk_pz_prepare with the same parameters; edge_std is float32 (O,I); fewer than two
+ * rows give NaN as torch.std does.
+ */
+size_t qk_edge_stats_scratch_bytes(const QkDesc* desc);
+int qk_pz_edge_stats(const QkDesc* desc, const void* x, const void* tables, size_t tables_bytes,
+                     int with_base_term, float* edge_std, void* scratch, size_t scratch_bytes,
+                     void* cuda_stream);
+
+/*
  * Solver plug-in contract (src/qkan/solver/_base.py:29-51, call site
  * src/qkan/qkan.py:699-714): per-edge activations postacts (B,O,I) in
  * io_dtype, and the matching backward from grad_postacts (B,O,I). Used by
@@ -205,7 +219,8 @@ int qk_pz_forward_noalloc(const QkDesc* desc, const void* x, const float* theta,
  * Developer overrides of the tile choice, process-wide; no counterpart in the reference (its batch-tile
  * heuristic, src/qkan/_kernel_utils.py:18-31, is fixed). 0 restores the library's own choice. On first use the
  * values are seeded once from the environment variables QK_BWD_GROUPS, QK_BWD_RPG, QK_BWD_RU, QK_BWD_OSPLIT,
- * QK_NO_XTRIG and QK_DEBUG; the launch path itself never reads the environment. Workspace sizes depend on the
+ * QK_NO_XTRIG, QK_DEBUG, QK_FWD_THREADS, QK_FWD_TB and QK_FWD_OT; the launch path itself never reads the
+ * environment. Workspace sizes depend on the
  * tile choice: query them after setting an override, and do not change one between a size query and its call.
  */
 enum QkDebugKey {
@@ -214,7 +229,10 @@ enum QkDebugKey {
     QK_DBG_BWD_RU = 2,     /* rows a thread keeps in flight (2 or 4) */
     QK_DBG_BWD_OSPLIT = 3, /* output slices of the backward (grid.z) */
     QK_DBG_NO_XTRIG = 4,   /* non-zero: frozen-preact forward uses the generic kernel */
-    QK_DBG_VERBOSE = 5     /* non-zero: print the chosen tiles to stderr */
+    QK_DBG_VERBOSE = 5,    /* non-zero: print the chosen tiles to stderr */
+    QK_DBG_FWD_THREADS = 6, /* threads per forward CTA (multiple of 32, <= 512); needs the next two as well */
+    QK_DBG_FWD_TB = 7,      /* batch rows per forward CTA (multiple of 32) */
+    QK_DBG_FWD_OT = 8       /* outputs per forward CTA */
 };
 void qk_debug_set(int key, int value);
 

@@ -25,7 +25,8 @@ QK_FAST_MEASURE = 2
 QK_USE_POSTACT_BIAS = 4
 QK_PRECISE_MATH = 8
 
-QK_DBG_BWD_GROUPS, QK_DBG_BWD_RPG, QK_DBG_BWD_RU, QK_DBG_BWD_OSPLIT, QK_DBG_NO_XTRIG, QK_DBG_VERBOSE = range(6)
+(QK_DBG_BWD_GROUPS, QK_DBG_BWD_RPG, QK_DBG_BWD_RU, QK_DBG_BWD_OSPLIT, QK_DBG_NO_XTRIG, QK_DBG_VERBOSE,
+ QK_DBG_FWD_THREADS, QK_DBG_FWD_TB, QK_DBG_FWD_OT) = range(9)
 
 QK_OK = 0
 QK_ERR_BAD_ARGUMENT = -1
@@ -51,6 +52,8 @@ SYMBOLS = {
     "qk_pz_prepare": (c_int, [_P] * 8 + [_P, c_size_t, _P]),
     "qk_pz_forward_prepared": (c_int, [_P, _P, _P, c_size_t, c_int, _P, _P]),
     "qk_pz_backward_prepared": (c_int, [_P, _P, _P, c_size_t, _P, _P, _P, c_int] + [_P] * 8 + [_P, c_size_t, _P]),
+    "qk_edge_stats_scratch_bytes": (c_size_t, [_P]),
+    "qk_pz_edge_stats": (c_int, [_P, _P, _P, c_size_t, c_int, _P, _P, c_size_t, _P]),
     "qk_debug_set": (None, [c_int, c_int]),
     "qk_noalloc_max_scratch_bytes": (c_size_t, []),
     "qk_noalloc_last_error": (c_char_p, []),

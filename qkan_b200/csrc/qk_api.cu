@@ -441,6 +441,39 @@ int qk_pz_backward_prepared(const QkDesc* desc, const void* x, const void* table
                                  static_cast<cudaStream_t>(stream));
 }
 
+size_t qk_edge_stats_scratch_bytes(const QkDesc* desc) {
+    if (check_desc(desc)) return 0;
+    if (empty(*desc)) return 256;
+    return qk::stats_scratch_bytes(desc->batch, desc->in_dim, desc->out_dim);
+}
+
+int qk_pz_edge_stats(const QkDesc* desc, const void* x, const void* tables, size_t tables_bytes,
+                     int with_base_term, float* edge_std, void* scratch, size_t scratch_bytes, void* stream) {
+    int rc = check_desc(desc);
+    if (rc) return rc;
+    const QkDesc& d = *desc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (no_edges(d)) return QK_OK;
+    if (!edge_std) return fail(QK_ERR_BAD_ARGUMENT, "edge_std is NULL");
+    if (d.batch == 0) {  // the deviation of no rows is not a number, as torch.std answers
+        cudaError_t e = cudaMemsetAsync(edge_std, 0xff, (size_t)d.out_dim * d.in_dim * sizeof(float), st);
+        if (e != cudaSuccess) return cuda_fail(e, "memset edge_std");
+        return QK_OK;
+    }
+    if (!x) return fail(QK_ERR_BAD_ARGUMENT, "x is NULL");
+    const Tables tl = tables_layout(d);
+    rc = check_buffer(tables, tables_bytes, tl.total, "tables");
+    if (rc) return rc;
+    rc = check_buffer(scratch, scratch_bytes, qk::stats_scratch_bytes(d.batch, d.in_dim, d.out_dim), "workspace");
+    if (rc) return rc;
+    cudaError_t e = qk::launch_edge_stats(
+        x, d.io_dtype, reinterpret_cast<const float*>(static_cast<const char*>(tables) + tl.table_off), d.batch,
+        d.in_dim, d.out_dim, qk::compiled_reps(d.ansatz, d.reps), (d.flags & QK_FAST_MEASURE) != 0,
+        with_base_term != 0, edge_std, static_cast<float*>(scratch), st);
+    if (e != cudaSuccess) return cuda_fail(e, "edge statistics launch");
+    return QK_OK;
+}
+
 void qk_debug_set(int key, int value) { qk::debug_set(key, value); }
 
 int qk_pz_forward(const QkDesc* desc, const void* x, const float* theta, const float* pw,

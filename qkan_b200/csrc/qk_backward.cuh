@@ -91,11 +91,26 @@ __device__ __forceinline__ float edge_backward(const EdgeFwd<R>& e, float x, flo
 
 constexpr int kGyChunk = 8;  // outputs whose grad_y columns are staged together
 
+// Register cap of the short circuits (up to 3 repetitions): two CTAs of 256 threads stay resident per SM and the
+// compiler spends the rest on scheduling; longer circuits were faster with the compiler's own choice. The cap,
+// the block-size bound beside it and the inlining of the column sums are a measured optimum of the instruction
+// schedule, not limits the code needs. Backward call at 65536 x 256 -> 256, 3 repetitions (ms): cap 96 with the
+// block-size bound and inlined sums 14.95; without the bound 15.25; sums out of line 15.42; cap 88 15.46,
+// 104 15.32, 112 15.00, 128 15.53.
+#ifndef QK_BWD_SHORT_MAXNREG
+#define QK_BWD_SHORT_MAXNREG 96
+#endif
+#ifdef QK_BWD_COLSUM_NOINLINE
+#define QK_COLSUM_LINKAGE static __device__ __noinline__
+#else
+#define QK_COLSUM_LINKAGE static __device__ __forceinline__
+#endif
+
 // Column sums of one batch tile's staged grad_y rows (the postact-bias terms need sum_b grad_y[b,o]): taken by
 // the CTAs of column block 0 only, one warp per output, lane-strided partial sums and a shuffle tree (fixed
-// order); finish_grads adds the tiles in order. Kept out of line so that the hot loop's register allocation
-// is the same with and without it.
-static __device__ __noinline__ void tile_column_sums(float* __restrict__ dst, const float* gy_s, int nch, int groups, int tb) {
+// order); finish_grads adds the tiles in order. (Inlined: measured 3 % faster at the headline shape than the
+// out-of-line call, through nothing but a different instruction schedule of the hot loop.)
+QK_COLSUM_LINKAGE void tile_column_sums(float* __restrict__ dst, const float* gy_s, int nch, int groups, int tb) {
     const int lane = threadIdx.x % kWarp, grp = threadIdx.x / kWarp;
     for (int c = grp; c < nch; c += groups) {
         float s = 0.f;
@@ -107,7 +122,7 @@ static __device__ __noinline__ void tile_column_sums(float* __restrict__ dst, co
 }
 
 template <int R, bool FAST, typename IO, bool EDGES, int RU, bool PRECISE, bool OSLICE>
-__global__ void __launch_bounds__(256, R <= 3 ? 2 : 0) backward_kernel(BwdArgs a) {
+__global__ void __launch_bounds__(256) __maxnreg__(R <= 3 ? QK_BWD_SHORT_MAXNREG : 255) backward_kernel(BwdArgs a) {
     constexpr int NACC = acc_rows(R);
     // floats per tile row: 32 (x, grad_x) pairs; a pair is one 64-bit access
     constexpr int ROW = 64;

@@ -132,6 +132,30 @@ __device__ __forceinline__ void precise_sincos(float a, float& s, float& c) {
     c = ((q + 1) & 2) ? -cc : cc;
 }
 
+// sin and cos on the FMA pipe at the special-function unit's accuracy (abs. error ~1.5e-7 for |a| up to a few
+// pi): reduction by pi with the round-to-nearest-integer constant, odd / even minimax polynomials on
+// [-pi/2, pi/2], sign from the parity of the multiple. 17 FP32 / integer instructions and no special-function
+// call: the forward is bound by that unit (2 calls per data gate), so it evaluates a share of its rows this way
+// to put its idle FMA issue slots to work.
+__device__ __forceinline__ void poly_sincos(float a, float& s, float& c) {
+    const float t = fmaf(a, 0.318309886183790672f, 12582912.0f);  // 1.5 * 2^23: the multiple lands in the low mantissa bits
+    const float j = t - 12582912.0f;
+    float r = fmaf(j, -3.14159274101257324f, a);
+    r = fmaf(j, 8.74227765734758577e-8f, r);  // (float)pi - pi
+    const unsigned sign = __float_as_uint(t) << 31;
+    const float z = r * r;
+    float ps = fmaf(z, 2.593941034e-06f, -1.980381325e-04f);
+    ps = fmaf(ps, z, 8.332978007e-03f);
+    ps = fmaf(ps, z, -1.666665547e-01f);
+    ps = fmaf(ps * z, r, r);
+    float pc = fmaf(z, 2.313151009e-05f, -1.385326930e-03f);
+    pc = fmaf(pc, z, 4.166365739e-02f);
+    pc = fmaf(pc, z, -4.999992083e-01f);
+    pc = fmaf(pc, z, 1.0f);
+    s = __uint_as_float(__float_as_uint(ps) ^ sign);
+    c = __uint_as_float(__float_as_uint(pc) ^ sign);
+}
+
 template <bool PRECISE>
 __device__ __forceinline__ void qk_sincos(float a, float& s, float& c) {
     if constexpr (PRECISE) {
@@ -237,7 +261,8 @@ __device__ __forceinline__ float real_forward(const EdgeFwd<0>& e, float x, floa
 
 // Forward of one edge for one batch row: returns the readout p (before bias and weight).
 // When KEEP is true the data-gate sin/cos and the final Bloch vector are returned for the backward.
-template <int R, bool FAST, bool KEEP, bool PRECISE>
+// POLY > 0: the first POLY data gates take their sin/cos from poly_sincos (FMA pipe) instead of the special-function unit.
+template <int R, bool FAST, bool KEEP, bool PRECISE, int POLY = 0>
 __device__ __forceinline__ float edge_forward(const EdgeFwd<R>& e, float x, float* cs, float* sn,
                                               float& vx, float& vy, float& vz, float& inv_rho,
                                               float& r) {
@@ -257,7 +282,10 @@ __device__ __forceinline__ float edge_forward(const EdgeFwd<R>& e, float x, floa
             vz = nz;
         }
         float s, c;
-        qk_sincos<PRECISE>(fmaf(e.pw[l], x, e.c[l]), s, c);  // merged Rz(pw_l x + pb_l + theta[l+1,0])
+        if (!PRECISE && l < POLY)
+            poly_sincos(fmaf(e.pw[l], x, e.c[l]), s, c);
+        else
+            qk_sincos<PRECISE>(fmaf(e.pw[l], x, e.c[l]), s, c);  // merged Rz(pw_l x + pb_l + theta[l+1,0])
         if (KEEP) {
             cs[l] = c;
             sn[l] = s;

@@ -13,13 +13,15 @@ constexpr int kGyChunkHost = 8;  // must match kGyChunk of the backward kernel
 
 // Developer overrides of the tile choice (0 = none). They are process-wide values set through qk_debug_set;
 // the first use seeds them, once, from the environment variables of the same names (QK_BWD_GROUPS, QK_BWD_RPG,
-// QK_BWD_RU, QK_BWD_OSPLIT, QK_NO_XTRIG, QK_DEBUG), so the launch path itself never reads the environment.
+// QK_BWD_RU, QK_BWD_OSPLIT, QK_NO_XTRIG, QK_DEBUG, QK_FWD_THREADS, QK_FWD_TB, QK_FWD_OT), so the launch path
+// itself never reads the environment.
 static std::atomic<int> g_debug[kDbgCount];
 static std::once_flag g_debug_once;
 
 static void debug_seed() {
     static const char* const names[kDbgCount] = {"QK_BWD_GROUPS", "QK_BWD_RPG", "QK_BWD_RU",
-                                                 "QK_BWD_OSPLIT", "QK_NO_XTRIG", "QK_DEBUG"};
+                                                 "QK_BWD_OSPLIT", "QK_NO_XTRIG", "QK_DEBUG",
+                                                 "QK_FWD_THREADS", "QK_FWD_TB", "QK_FWD_OT"};
     for (int k = 0; k < kDbgCount; ++k) {
         const char* v = getenv(names[k]);
         g_debug[k].store(v && *v ? (atoi(v) != 0 ? atoi(v) : 1) : 0, std::memory_order_relaxed);
@@ -62,6 +64,18 @@ FwdCfg choose_fwd_cfg(const QkDesc& d, bool edges, bool base, bool xtrig) {
     const int ipad = round_up(d.in_dim, 32);
     FwdCfg best{};
     double best_cost = -1.0;
+    const int f_threads = tune_int(kDbgFwdThreads, 0), f_tb = tune_int(kDbgFwdTb, 0), f_ot = tune_int(kDbgFwdOt, 0);
+    if (f_threads > 0 && f_tb > 0 && f_ot > 0) {  // developer override
+        FwdCfg c{};
+        c.threads = f_threads;
+        c.ich = ipad < 256 ? ipad : 256;
+        c.tb = round_up(f_tb, 32);
+        c.ot = d.out_dim < f_ot ? d.out_dim : f_ot;
+        c.grid_b = (d.batch + c.tb - 1) / c.tb;
+        c.grid_o = (d.out_dim + c.ot - 1) / c.ot;
+        c.smem = (size_t)c.tb * c.ich * 4 * ((xtrig ? 2 : 1) + (base ? 1 : 0)) + (edges ? 0 : (size_t)c.ot * (c.tb + 1) * 4);
+        if (c.smem <= (size_t)kSmemCap) return c;
+    }
     for (int tb : {64, 32}) {
         for (int ot = 256; ot >= 1; ot /= 2) {
             FwdCfg c{};

@@ -33,10 +33,29 @@ __device__ __forceinline__ float transpose_reduce32(float (&v)[32], int lane) {
 
 __device__ __forceinline__ float silu_f(float v) { return v / (1.f + expf(-v)); }
 
+// One row in QK_FWD_POLY_EVERY of a lane's 32-row block evaluates the sin/cos of its first QK_FWD_POLY_GATES data
+// gates on the FMA pipe (poly_sincos) instead of the special-function unit, which bounds this kernel; 0 switches
+// that off. Measured at 65536 x 256 -> 256, 3 repetitions (forward, ms): off 8.72; one gate of every 4th row 8.57,
+// of every 3rd 8.66, of every 2nd 8.61, of every row 9.12; two gates of every 4th row 8.58, of every 2nd 9.14;
+// all gates of every 8th row 8.66, of every 6th 8.72, of every 4th 8.86, of every 3rd 9.06. The unit is 84 % busy
+// without it, yet moving more than a twelfth of the calls off it loses again: the kernel is as much bound by
+// its queue to that unit, which the shuffles and shared-memory reads share, as by the unit itself.
+#ifndef QK_FWD_POLY_EVERY
+#define QK_FWD_POLY_EVERY 4
+#endif
+#ifndef QK_FWD_POLY_GATES
+#define QK_FWD_POLY_GATES 1
+#endif
+#ifdef QK_FWD_MAXNREG
+#define QK_FWD_REGCAP __maxnreg__(QK_FWD_MAXNREG)
+#else
+#define QK_FWD_REGCAP __launch_bounds__(512)
+#endif
+
 // XTRIG: the x tile holds (cos x, sin x) pairs and the data gates use the angle-addition form
 // (frozen preacts, see edge_forward_xtrig).
 template <int R, bool FAST, typename IO, bool BASE, bool EDGES, bool PRECISE, bool XTRIG>
-__global__ void __launch_bounds__(512) forward_kernel(FwdArgs a) {
+__global__ void QK_FWD_REGCAP forward_kernel(FwdArgs a) {
     extern __shared__ __align__(16) float smem[];
     const int tb = a.cfg.tb, ot = a.cfg.ot, ich = a.cfg.ich;
     const int ldy = tb + 1;
@@ -93,7 +112,11 @@ __global__ void __launch_bounds__(512) forward_kernel(FwdArgs a) {
                         } else {
                             float xv = x_s[(rg + r) * ich + col];
                             float vx, vy, vz, ir, rr;
-                            p = edge_forward<R, FAST, false, PRECISE>(e, xv, nullptr, nullptr, vx, vy, vz, ir, rr);
+                            constexpr int kPolyGates = R < QK_FWD_POLY_GATES ? R : QK_FWD_POLY_GATES;
+                            if (QK_FWD_POLY_EVERY > 0 && (r % (QK_FWD_POLY_EVERY > 0 ? QK_FWD_POLY_EVERY : 1)) == QK_FWD_POLY_EVERY - 1)
+                                p = edge_forward<R, FAST, false, PRECISE, kPolyGates>(e, xv, nullptr, nullptr, vx, vy, vz, ir, rr);
+                            else
+                                p = edge_forward<R, FAST, false, PRECISE>(e, xv, nullptr, nullptr, vx, vy, vz, ir, rr);
                         }
                         if (EDGES) {
                             v[r] = p;

@@ -106,7 +106,7 @@ struct BaseBwdArgs {
 FwdCfg choose_fwd_cfg(const QkDesc& d, bool edges, bool base, bool xtrig);
 
 // Developer overrides (qk_debug_set in the C ABI; first use also reads the QK_* environment variables once).
-enum DebugKey { kDbgBwdGroups = 0, kDbgBwdRpg, kDbgBwdRu, kDbgBwdOsplit, kDbgNoXtrig, kDbgVerbose, kDbgCount };
+enum DebugKey { kDbgBwdGroups = 0, kDbgBwdRpg, kDbgBwdRu, kDbgBwdOsplit, kDbgNoXtrig, kDbgVerbose, kDbgFwdThreads, kDbgFwdTb, kDbgFwdOt, kDbgCount };
 int debug_get(int key);
 void debug_set(int key, int value);
 
@@ -132,6 +132,10 @@ int base_rows_per_cta(int batch, int in_dim);
 cudaError_t launch_base_backward(const BaseBwdArgs& a, int io_dtype, cudaStream_t st);
 
 cudaError_t launch_prep(const PrepArgs& a, cudaStream_t st);
+// per-edge standard deviation over the batch of the edge outputs (qk_stats.cu); scratch: stats_scratch_bytes()
+size_t stats_scratch_bytes(int batch, int in_dim, int out_dim);
+cudaError_t launch_edge_stats(const void* x, int io_dtype, const float* table, int batch, int in_dim, int out_dim,
+                              int rk, bool fast, bool base, float* out_std, float* scratch, cudaStream_t st);
 cudaError_t launch_finish(const FinishArgs& a, cudaStream_t st);
 // gx[n] = sum over the output slices of part[s][n], in slice order, stored in the I/O dtype
 cudaError_t launch_sum_gx(const float* part, void* gx, int io_dtype, size_t n, int nslices, cudaStream_t st);

@@ -224,6 +224,27 @@ def backward_prepared(prep: PreparedLayer, x: torch.Tensor, gy: torch.Tensor, *,
     return out
 
 
+def edge_stats(prep: PreparedLayer, x: torch.Tensor) -> torch.Tensor:
+    """Unbiased standard deviation over the batch of every edge's output, ``(O,I)`` float32 (``qk_pz_edge_stats``).
+
+    Equal to ``torch.std(forward_no_sum(x), dim=0)`` of the reference (``src/qkan/qkan.py:835-891, 1287-1292``)
+    without the ``(B,O,I)`` tensor; no autograd (the reference computes it under ``no_grad`` as well).
+    """
+    lib = _abi.load()
+    _require_cuda(x, "x")
+    x = x.detach().contiguous()
+    desc = prep.desc(x)
+    out = torch.empty((desc.out_dim, desc.in_dim), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        nbytes = lib.qk_edge_stats_scratch_bytes(_abi.desc_pointer(desc))
+        ws = _workspace(x.device, nbytes)
+        rc = lib.qk_pz_edge_stats(_abi.desc_pointer(desc), _ptr(x), _ptr(prep.tables), prep.tables.numel(),
+                                  int(prep.has_base), _ptr(out), _ptr(ws), ws.numel(),
+                                  torch.cuda.current_stream(x.device).cuda_stream)
+    _abi.check(rc, "qk_pz_edge_stats")
+    return out
+
+
 def layer_forward(x, theta, pw, pb, postw, postb=None, basew=None, mask=None, *,
                   preact_trainable: bool, fast_measure: bool = True,
                   use_postact_bias: bool = False, ansatz: str = "pz_encoding",

@@ -46,6 +46,10 @@ def chunk_spans(batch: int, n_chunks: int, row_align: int = 148 * 64):
 class HostLayerPipeline:
     """Chunked, stream-overlapped ``y, grad_x, parameter gradients`` from host-resident ``x, grad_y``."""
 
+    #: library launches of one step(): 1 set-up + (forward + backward + finish) per chunk
+    def launches_per_step(self) -> int:
+        return 1 + 3 * len(self.spans)
+
     def __init__(self, batch: int, in_dim: int, out_dim: int, reps: int, device, *, n_chunks: int = 3,
                  dtype: torch.dtype = torch.float32, preact_trainable: bool = True,
                  fast_measure: bool = True, use_postact_bias: bool = True, ansatz: str = "pz_encoding",
@@ -84,6 +88,9 @@ class HostLayerPipeline:
         synchronisation of the current stream, or after ``torch.cuda.synchronize()``."""
         compute = torch.cuda.current_stream(self.device)
         p = params
+        # the per-edge tables are built once per step and serve every chunk (they have no batch axis)
+        prep = qf.prepare_layer(p["theta"], p["pw"], p["pb"], p["postw"], p.get("postb"), p.get("basew"),
+                                p.get("mask"), in_dim=self.dx[0].shape[1], **self.cfg)
         for k, (b, e) in enumerate(self.spans):
             with torch.cuda.stream(self.s_in):
                 if not self._first:
@@ -94,12 +101,9 @@ class HostLayerPipeline:
             compute.wait_event(self.ev_in[k])
             if not self._first:
                 compute.wait_event(self.ev_free[k])  # the previous step's y and grad_x of this chunk have left the device
-            y = qf.layer_forward(self.dx[k], p["theta"], p["pw"], p["pb"], p["postw"], p.get("postb"),
-                                 p.get("basew"), p.get("mask"), out=self.dy[k], **self.cfg)
+            y = qf.forward_prepared(prep, self.dx[k], out=self.dy[k])
             outs = dict(self.chunk_buckets[k].views, x=self.dgx[k])
-            qf.layer_backward(self.dx[k], p["theta"], p["pw"], p["pb"], p["postw"], p.get("postb"),
-                              p.get("basew"), p.get("mask"), self.dgy[k], out=outs,
-                              want=tuple(outs), **self.cfg)
+            qf.backward_prepared(prep, self.dx[k], self.dgy[k], out=outs, want=tuple(outs))
             self.ev_done[k].record(compute)
             with torch.cuda.stream(self.s_out):
                 self.s_out.wait_event(self.ev_done[k])

@@ -303,6 +303,27 @@ class QKANLayer(nn.Module):
         return ((postacts + self._as_oi(self.postact_bias)) * self._as_oi(self.postact_weights)[None]
                 + base) * self._as_oi(self.mask)[None]
 
+    @torch.no_grad()
+    def edge_output_std(self, x: torch.Tensor) -> torch.Tensor:
+        """``torch.std(forward_no_sum(x), dim=0)``, shape ``(O, I)``, computed inside the kernels.
+
+        This is the per-edge activation scale the model's ``save_act`` pass needs
+        (``src/qkan/qkan.py:1287-1292``); the ``(B, O, I)`` tensor the reference forms for it is never
+        allocated. Base activations other than silu are not fused, so they take the ``forward_no_sum`` route.
+        """
+        assert x.shape[1] == self.in_dim, "Invalid input dimension"
+        self._check_solver()
+        has_base = self.ba_trainable or self._bw_is_nonzero or bool(self.base_weight.requires_grad)
+        if has_base and not isinstance(self.base_activation, nn.SiLU):
+            return torch.std(self.forward_no_sum(x), dim=0)
+        theta, pw, pb = self._kernel_params()
+        mask = None if self._mask_is_identity else self._as_oi(self.mask)
+        prep = qf.prepare_layer(theta, pw, pb, self._as_oi(self.postact_weights), None,
+                                self._as_oi(self.base_weight) if has_base else None, mask, in_dim=self.in_dim,
+                                preact_trainable=self.preact_trainable, fast_measure=self.fast_measure,
+                                use_postact_bias=False, ansatz=self.ansatz)
+        return qf.edge_stats(prep, x).to(self.p_dtype)
+
     def get_subset(self, in_id, out_id) -> "QKANLayer":
         """Smaller layer holding the selected input / output neurons (``src/qkan/qkan.py:893-957``)."""
         sub = QKANLayer(len(in_id), len(out_id), reps=self.reps, device=self.device, solver=self.solver,

@@ -77,6 +77,10 @@ class QKAN(nn.Module):
                 c_dtype=c_dtype, p_dtype=p_dtype, seed=seed, solver_kwargs=self.solver_kwargs,
                 p_dim=p_dim, checkpoint_reps=checkpoint_reps, theta_init=theta_init))
         self.is_batchnorm, self.is_map, self.hidden = is_batchnorm, is_map, hidden
+        # save_act keeps per-edge STATISTICS (computed inside the kernels). The per-sample edge tensors
+        # dr_preacts / dr_postacts of shape (B, O, I) that the reference also stores are only materialised
+        # when this is switched on (the plotting tools that read them are not part of this package).
+        self.keep_edge_acts = bool(kwargs.get("keep_edge_acts", False))
         if is_map:
             self.layers.append(nn.Linear(width[-2], hidden, device=device, dtype=p_dtype))
             self.layers.append(nn.SiLU())
@@ -121,18 +125,21 @@ class QKAN(nn.Module):
         for layer in self.layers:
             track = self.save_act and isinstance(layer, QKANLayer)
             if track:
+                x_in = x
                 self.subnode_actscale.append(torch.std(x, dim=0).detach())
-                preacts = x[:, None, :].expand(rows, layer.out_dim, layer.in_dim)
-                postacts = layer.forward_no_sum(x)
+                # per-edge standard deviation over the batch, from the kernels: no (B, O, I) tensor
+                output_range = layer.edge_output_std(x)
             x = layer(x)
             if track:
-                input_range = torch.std(preacts, dim=0) + 0.1
-                output_range = torch.std(postacts, dim=0)
+                # every output sees the same inputs, so the (O, I) input range is one row repeated; it keeps
+                # its autograd link to the previous layers, as in the reference
+                input_range = (torch.std(x_in, dim=0) + 0.1)[None, :].expand(layer.out_dim, layer.in_dim)
                 self.edge_actscale.append(output_range)
                 self.acts_scale.append((output_range / input_range).detach())
                 self.acts_scale_dr.append(output_range / input_range)
-                self.dr_preacts.append(preacts.detach())
-                self.dr_postacts.append(postacts.detach())
+                if self.keep_edge_acts:
+                    self.dr_preacts.append(x_in.detach()[:, None, :].expand(rows, layer.out_dim, layer.in_dim))
+                    self.dr_postacts.append(layer.forward_no_sum(x_in).detach())
                 self.acts.append(x.detach())
         if self.norm_out:
             x = F.normalize(x, p=self.norm_out, dim=1)

@@ -3,7 +3,7 @@
 Usage (only where the reference checkout is mounted; the fixtures are committed so
 nothing at test time needs it):
 
-    python tests/golden/make_golden.py /path/to/reference [layer|ansatz|init|fit]
+    python tests/golden/make_golden.py /path/to/reference [layer|ansatz|group|init|fit|act]
 
 The reference package imports ``matplotlib`` unconditionally (``src/qkan/qkan.py:33``)
 for its plotting helpers; an empty stand-in module is registered before the import,
@@ -21,6 +21,8 @@ What is written:
 * ``init_cases.npz`` — seeded parameter initialisations (``state_dict`` tensors).
 * ``fit_case.npz`` — the 1-D function-fit configuration: dataset, seeded initial
   prediction / loss / gradients, and the LBFGS loss trajectory of the reference.
+* ``act_cases.npz`` — ``save_act`` statistics of small models (per-layer ``acts_scale``, ``edge_actscale``,
+  ``subnode_actscale``) and the regulariser ``get_reg`` built from them.
 """
 from __future__ import annotations
 
@@ -250,6 +252,41 @@ def fit_case(qkan, torch):
     np.savez_compressed(os.path.join(HERE, "fit_case.npz"), **out)
 
 
+def act_cases(qkan, torch):
+    """save_act statistics of the reference's QKAN.forward (src/qkan/qkan.py:1280-1302) and its regulariser
+    (src/qkan/qkan.py:1445-1550): the model's state, the input, and per layer acts_scale / edge_actscale /
+    subnode_actscale, plus get_reg for the three forward metrics."""
+    out = {}
+    specs = {
+        "mlp_base": dict(width=[5, 4, 3], reps=2, seed=3, ba_trainable=True, save_act=True),
+        "mlp_trainable": dict(width=[6, 3, 2], reps=3, seed=5, preact_trainable=True, preact_init=True,
+                              postact_weight_trainable=True, postact_bias_trainable=True, save_act=True),
+        "born_nobase": dict(width=[4, 5], reps=1, seed=9, fast_measure=False, save_act=True),
+    }
+    for name, kw in specs.items():
+        model = qkan.QKAN(**kw)
+        g = torch.Generator().manual_seed(77)
+        with torch.no_grad():  # make the (O,I) epilogue tensors non-trivial
+            for layer in model.layers:
+                layer.postact_weights.add_(0.3 * torch.randn(layer.postact_weights.shape, generator=g))
+                layer.postact_bias.add_(0.2 * torch.randn(layer.postact_bias.shape, generator=g))
+                layer._pb_is_nonzero = True
+        x = torch.rand(64, kw["width"][0], generator=g) * 2 - 1
+        y = model(x)
+        out[f"{name}/x"] = x.numpy()
+        out[f"{name}/y"] = y.detach().numpy()
+        for k, v in model.state_dict().items():
+            out[f"{name}/state/{k}"] = v.detach().numpy()
+        for l in range(len(model.acts_scale)):
+            out[f"{name}/acts_scale/{l}"] = model.acts_scale[l].detach().numpy()
+            out[f"{name}/edge_actscale/{l}"] = model.edge_actscale[l].detach().numpy()
+            out[f"{name}/subnode_actscale/{l}"] = model.subnode_actscale[l].detach().numpy()
+        for metric in ("edge_forward_dr_n", "edge_forward_sum", "edge_forward_dr_u"):
+            out[f"{name}/reg/{metric}"] = np.array(float(model.get_reg(metric, 1.0, 2.0, 0.1, 0.05)))
+    out["names"] = np.array(list(specs))
+    np.savez_compressed(os.path.join(HERE, "act_cases.npz"), **out)
+
+
 def main():
     ref_root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("QKAN_REFERENCE_ROOT", "")
     if not ref_root or not os.path.isdir(ref_root):
@@ -269,6 +306,8 @@ def main():
         init_cases(qkan, torch)
     if only in ("all", "fit"):
         fit_case(qkan, torch)
+    if only in ("all", "act"):
+        act_cases(qkan, torch)
     print("wrote", sorted(p for p in os.listdir(HERE) if p.endswith(".npz")))
 
 

@@ -318,3 +318,66 @@ def test_train_loop_with_a_closure_driven_composite_optimizer():
     res = model.train_(ds, optimizer=opt, steps=6, verbose=False)
     assert len(res["train_loss"]) == 6 and opt.lbfgs is not None
     assert float(res["train_loss"][-1]) < float(res["train_loss"][0])
+
+
+ACT_SPECS = {
+    "mlp_base": dict(width=[5, 4, 3], reps=2, seed=3, ba_trainable=True, save_act=True),
+    "mlp_trainable": dict(width=[6, 3, 2], reps=3, seed=5, preact_trainable=True, preact_init=True,
+                          postact_weight_trainable=True, postact_bias_trainable=True, save_act=True),
+    "born_nobase": dict(width=[4, 5], reps=1, seed=9, fast_measure=False, save_act=True),
+}
+
+
+@pytest.mark.parametrize("name", sorted(ACT_SPECS))
+def test_save_act_statistics_and_regulariser_match_reference(name):
+    """QKAN.forward(save_act=True): per-layer acts_scale / edge_actscale / subnode_actscale and get_reg against the
+    reference's own values (fixture made by tests/golden/make_golden.py), with the per-edge deviations coming from
+    the in-kernel statistics instead of a (B, O, I) tensor."""
+    gold = np.load(f"{GOLDEN}/act_cases.npz")
+    model = QKAN(device="cuda", **ACT_SPECS[name])
+    state = {k[len(name) + 7:]: torch.as_tensor(gold[k]) for k in gold.files if k.startswith(name + "/state/")}
+    model.load_state_dict(state)
+    x = torch.as_tensor(gold[name + "/x"], device="cuda")
+    y = model(x)
+    assert nerr(y.detach().cpu().numpy(), gold[name + "/y"]) <= TOL_F32
+    assert not model.dr_postacts and not model.dr_preacts  # nothing of size (B, O, I) is kept by default
+    for l in range(len(model.acts_scale)):
+        for key, got in (("acts_scale", model.acts_scale[l]), ("edge_actscale", model.edge_actscale[l]),
+                         ("subnode_actscale", model.subnode_actscale[l])):
+            want = gold[f"{name}/{key}/{l}"]
+            assert nerr(got.detach().cpu().numpy(), want) <= 2e-5, f"{key}[{l}]"
+    for metric in ("edge_forward_dr_n", "edge_forward_sum", "edge_forward_dr_u"):
+        reg = float(model.get_reg(metric, 1.0, 2.0, 0.1, 0.05))
+        want = float(gold[f"{name}/reg/{metric}"])
+        assert abs(reg - want) <= 2e-5 * abs(want), metric
+    # the opt-in keeps the reference's per-sample edge tensors too
+    model.keep_edge_acts = True
+    model(x)
+    assert model.dr_postacts[0].shape == (x.shape[0], model.width[1], model.width[0])
+    assert nerr(torch.std(model.dr_postacts[0], dim=0).cpu().numpy(), gold[f"{name}/edge_actscale/0"]) <= 2e-5
+
+
+def test_edge_statistics_at_transformer_width_use_no_batch_by_edge_tensor():
+    """8192 x 768 -> 768 (the HQKANsformer-shaped layer): the statistics pass peaks at a few hundred MB where
+    the (B, O, I) tensor alone would take 19 GB, and agrees with torch.std over forward_no_sum on a slice of outputs."""
+    layer = QKANLayer(768, 768, reps=2, device="cuda", ba_trainable=True, seed=1)
+    x = torch.randn(8192, 768, device="cuda").clamp_(-3, 3)
+    with torch.no_grad():
+        layer.postact_weights.mul_(torch.rand_like(layer.postact_weights) + 0.5)
+    layer.edge_output_std(x[:64])  # warm the allocator and the kernels
+    torch.cuda.synchronize()
+    torch.cuda.reset_peak_memory_stats()
+    before = torch.cuda.memory_allocated()
+    got = layer.edge_output_std(x)
+    torch.cuda.synchronize()
+    peak = torch.cuda.max_memory_allocated() - before
+    assert peak < 512 * 2**20, f"statistics pass peaked at {peak / 2**20:.0f} MiB"
+    outs = [0, 5, 383, 767]
+    sub = layer.get_subset(list(range(768)), outs)
+    want = torch.std(sub.forward_no_sum(x), dim=0)
+    assert nerr(got[outs].cpu().numpy(), want.cpu().numpy()) <= 2e-5
+    # ragged batch, bf16 activations
+    xb = x[:1000].to(torch.bfloat16)
+    gb = layer.edge_output_std(xb)
+    wb = torch.std(sub.forward_no_sum(xb.float()), dim=0)
+    assert nerr(gb[outs].float().cpu().numpy(), wb.cpu().numpy()) <= 1e-3
