@@ -16,7 +16,8 @@ NCCL all-reduce per step inside the timed region.
 Other workloads (``--config``): ``bf16_sweep`` (batch 8192, square layers 512 / 1024 / 2048, reps 1 / 2 / 4 / 8,
 bfloat16 activations), ``mnist`` (QKAN [784,128,10] Adam training step, batch 1024 per GPU) and ``hqkan``
 (a stack of twelve 768 -> 768 layers, reps 2, bfloat16 activations, 8192 rows per GPU, per-layer gradient
-all-reduce overlapped with the backward). Each prints one JSON line of the same form.
+all-reduce overlapped with the backward) and ``hqkan_block`` (the launch-bound hybrid block, eager and as a
+CUDA graph). Each prints one JSON line of the same form.
 
 Baselines. ``--impl reference`` times the reference package's own ``exact`` solver (torch, CPU, all host
 cores) on a bounded row sample of the same layer; the default run carries the same measurement as
@@ -71,13 +72,13 @@ PEAK_ISSUE = SM_COUNT * FP32_LANES * NOMINAL_GHZ * 1e-3  # 37.22 Tlane-op/s
 def backward_dram_bytes(rows: int, in_dim: int, out_dim: int, reps: int):
     """DRAM bytes of one backward_kernel launch, from one ncu capture scaled by the rows processed.
 
-    Captured: 16384 x 256 -> 256, reps 3, float32, 256-row tiles: dram read 52.17 MB, write 161.63 MB. The
+    Captured: 16384 x 256 -> 256, reps 3, float32, 256-row tiles: dram read 51.40 MB, write 162.19 MB. The
     traffic is x, grad_y, grad_x (algorithmic) plus the per-batch-tile gradient partials the kernel writes for
     the finishing kernel (not algorithmic), all proportional to the rows. Other shapes have no capture: None.
     """
     if (in_dim, out_dim, reps) != (256, 256, 3) or rows < 4096:
         return None
-    return int((52_166_912 + 161_625_344) * rows / 16384)
+    return int((51_401_472 + 162_188_032) * rows / 16384)
 
 
 def issue_roofline_seconds(edges: float, reps: int, which: str, ghz: float = NOMINAL_GHZ,
@@ -882,18 +883,76 @@ def run_hqkan(run: Run):
     return 0
 
 
+def count_kernels(torch, fn):
+    """(library kernels, all kernels) launched by one call of fn, from torch's profiler."""
+    from torch.profiler import ProfilerActivity, profile
+
+    fn()
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        fn()
+        torch.cuda.synchronize()
+    names = [e.name for e in prof.events() if str(e.device_type).endswith("CUDA") and "memcpy" not in e.name.lower()
+             and "memset" not in e.name.lower()]
+    return sum(1 for n in names if "qk::" in n), len(names)
+
+
+def run_hqkan_block(run: Run):
+    """The launch-bound regime: the hybrid block Linear(768 -> w) -> QKAN[w, w] -> Linear(w -> 768) in bfloat16
+    (qkan_b200.FusedHQKAN, w = 10, one repetition), forward + loss + backward, eager and captured in a CUDA graph."""
+    torch, args, dev, rank = run.torch, run.args, run.dev, run.rank
+    from qkan_b200 import FusedHQKAN
+    from qkan_b200.graph import make_graphed_train_step
+
+    table = []
+    for rows in (8192, 1024):
+        torch.manual_seed(0)
+        block = FusedHQKAN(768, 10, reps=1, device=dev)
+        x = torch.randn(rows, 768, device=dev, dtype=torch.bfloat16)
+        tgt = torch.randn(rows, 768, device=dev, dtype=torch.bfloat16)
+        loss_fn = lambda y, t: torch.nn.functional.mse_loss(y.float(), t.float())  # noqa: E731
+        opt = torch.optim.SGD(block.parameters(), lr=0.0)
+
+        def eager(mark=lambda: None):
+            block.zero_grad(set_to_none=True)
+            loss_fn(block(x), tgt).backward()
+
+        lib_k, all_k = count_kernels(torch, eager)
+        eager_ms = run.time_steps(eager, args.steps, args.warmup)[0] / args.steps
+        graphed = make_graphed_train_step(block, x, tgt, loss_fn, opt)
+        graph_ms = run.time_steps(lambda mark: graphed(x, tgt), args.steps, args.warmup)[0] / args.steps
+        table.append({"rows": rows, "eager_us": 1e3 * eager_ms, "graphed_us": 1e3 * graph_ms,
+                      "library_launches_per_step": lib_k, "all_kernels_per_step": all_k})
+    if rank == 0:
+        edges = sum(r["rows"] for r in table) * 100
+        ms = sum(r["graphed_us"] for r in table) * 1e-3
+        line = {
+            "metric": METRIC, "value": edges / (ms * 1e-3), "unit": UNIT, "n_gpus": run.world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms / len(table), "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "hybrid block Linear(768->10) -> QKAN[10,10] reps 1 -> Linear(10->768), bf16, "
+                                   "forward + MSE + backward at 8192 and 1024 rows, eager and CUDA-graph replay",
+                       "l2": "flushed between timed steps (256 MB write)",
+                       "library_kernels": "prep, forward, backward, base_backward, finish_grads"},
+            "rows": table, "gpu_launches": sum(r["library_launches_per_step"] for r in table) * args.steps,
+        }
+        print(json.dumps(line))
+    run.finish()
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=("b200", "reference"), default="b200")
-    ap.add_argument("--config", choices=("layer", "bf16_sweep", "mnist", "hqkan"), default="layer",
+    ap.add_argument("--config", choices=("layer", "bf16_sweep", "mnist", "hqkan", "hqkan_block"), default="layer",
                     help="workload; only the default is the benchmark line")
     ap.add_argument("--scaling", choices=("weak", "strong"), default="weak")
     ap.add_argument("--cpu-rows", type=int, default=1024, help="rows of the C-port CPU sample")
     ap.add_argument("--cpu-ref-rows", type=int, default=192, help="rows of the reference `exact` CPU sample")
-    ap.add_argument("--ref-rows", type=int, default=256, help="rows per step of --impl reference")
+    ap.add_argument("--ref-rows", type=int, default=128, help="rows per step of --impl reference")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-baselines", action="store_true", help="skip the reference's GPU solvers (profiling runs)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
@@ -912,7 +971,8 @@ def main():
     if args.impl == "reference":
         return run_reference(args)
     run = Run(args)
-    return {"layer": run_layer, "bf16_sweep": run_bf16_sweep, "mnist": run_mnist, "hqkan": run_hqkan}[args.config](run)
+    return {"layer": run_layer, "bf16_sweep": run_bf16_sweep, "mnist": run_mnist, "hqkan": run_hqkan,
+            "hqkan_block": run_hqkan_block}[args.config](run)
 
 
 if __name__ == "__main__":

@@ -92,7 +92,9 @@ __device__ __forceinline__ float edge_backward(const EdgeFwd<R>& e, float x, flo
 constexpr int kGyChunk = 8;  // outputs whose grad_y columns are staged together
 
 // Register cap of the short circuits (up to 3 repetitions): two CTAs of 256 threads stay resident per SM and the
-// compiler spends the rest on scheduling; longer circuits were faster with the compiler's own choice. The cap,
+// compiler spends the rest on scheduling; 4 to 8 repetitions are capped at 128 (still two CTAs: uncapped, the
+// 8-repetition kernel took 152 registers, lost its second CTA and a fifth of its speed); the padded 12- and
+// 16-repetition instantiations need more than that. The cap,
 // the block-size bound beside it and the inlining of the column sums are a measured optimum of the instruction
 // schedule, not limits the code needs. Backward call at 65536 x 256 -> 256, 3 repetitions (ms): cap 96 with the
 // block-size bound and inlined sums 14.95; without the bound 15.25; sums out of line 15.42; cap 88 15.46,
@@ -122,7 +124,7 @@ QK_COLSUM_LINKAGE void tile_column_sums(float* __restrict__ dst, const float* gy
 }
 
 template <int R, bool FAST, typename IO, bool EDGES, int RU, bool PRECISE, bool OSLICE>
-__global__ void __launch_bounds__(256) __maxnreg__(R <= 3 ? QK_BWD_SHORT_MAXNREG : 255) backward_kernel(BwdArgs a) {
+__global__ void __launch_bounds__(256) __maxnreg__(R <= 3 ? QK_BWD_SHORT_MAXNREG : (R <= 8 ? 128 : 255)) backward_kernel(BwdArgs a) {
     constexpr int NACC = acc_rows(R);
     // floats per tile row: 32 (x, grad_x) pairs; a pair is one 64-bit access
     constexpr int ROW = 64;

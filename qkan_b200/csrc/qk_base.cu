@@ -108,7 +108,10 @@ __global__ void __launch_bounds__(kBaseWarps * kWarp, 3) base_backward_kernel(Ba
                 const float v = ld_as_float(x + at);
                 const float sg = sigmoid_f(v);
                 const float dsl = sg * (1.f + v * (1.f - sg));
-                st_from_float(gx + at, fmaf(dsl, gxb[r], ld_as_float(gx + at)));
+                // grad_x is read and written by this kernel: a plain load (the read-only path is for data the
+                // kernel never writes). With bfloat16 activations the circuit share was rounded once when the
+                // backward stored it and the sum is rounded again here (half an ulp each, inside the bf16 bound).
+                st_from_float(gx + at, fmaf(dsl, gxb[r], ld_rw_as_float(gx + at)));
             }
         }
     }

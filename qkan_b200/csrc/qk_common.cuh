@@ -87,6 +87,9 @@ template <>
 __device__ __forceinline__ float ld_as_float<__nv_bfloat16>(const __nv_bfloat16* p) {
     return __bfloat162float(__ldg(p));
 }
+// plain (coherent) loads for buffers the same kernel also writes
+__device__ __forceinline__ float ld_rw_as_float(const float* p) { return *p; }
+__device__ __forceinline__ float ld_rw_as_float(const __nv_bfloat16* p) { return __bfloat162float(*p); }
 template <typename T>
 __device__ __forceinline__ void st_from_float(T* p, float v);
 template <>

@@ -90,9 +90,25 @@ class QKANLayer(nn.Module):
         self.is_batchnorm = is_batchnorm
         self.fast_measure = fast_measure
         self.seed = seed
-        # the kernels always compute in float32; a complex c_dtype maps to its real counterpart
-        # exactly as the reference does for its fused solvers (src/qkan/qkan.py:203-211)
-        self.c_dtype = {torch.complex64: torch.float32, torch.complex128: torch.float64}.get(c_dtype, c_dtype)
+        # c_dtype, the reference's "compute dtype" (src/qkan/qkan.py:203-211, src/qkan/solver/cute/cute_ops.py:191-231):
+        #   complex64 / float32 (default)  -> float32 activations in and out of the kernels;
+        #   complex128 / float64           -> accepted, computed in float32 (the kernels have no float64 path);
+        #   bfloat16                       -> activations cross the kernel boundary as bfloat16 (x, y, their
+        #                                     gradients), as in the reference's bf16 mode; theta, preacts and all
+        #                                     accumulation stay float32 here (the reference rounds theta to bf16);
+        #   float8_e4m3fn                  -> the same as bfloat16: in the reference this value only selects fp8
+        #                                     storage of the backward's state checkpoints
+        #                                     (src/qkan/csrc/cute_kernels.cu:1283-1292), and this backward keeps no
+        #                                     checkpoints at all (it sweeps one torque vector back), so there is
+        #                                     nothing left for the value to change.
+        known = {torch.complex64: torch.float32, torch.complex128: torch.float64, torch.float32: torch.float32,
+                 torch.float64: torch.float64, torch.bfloat16: torch.bfloat16,
+                 torch.float8_e4m3fn: torch.float8_e4m3fn}
+        if c_dtype not in known:
+            raise ValueError(f"c_dtype {c_dtype} is not supported: use complex64 / float32, complex128 / float64, "
+                             "bfloat16 or float8_e4m3fn")
+        self.c_dtype = known[c_dtype]
+        self._io_bf16 = self.c_dtype in (torch.bfloat16, torch.float8_e4m3fn)
         self.p_dtype = p_dtype
         self.preact_trainable = preact_trainable
         self.preact_init = preact_init
@@ -114,7 +130,7 @@ class QKANLayer(nn.Module):
             self._theta_natural_shape = (*group, reps + 1, 1)
         else:  # "real": no final layer; the reference also pins its compute dtype to bfloat16 here
             self._theta_natural_shape = (*group, reps, 1)
-            self.c_dtype = torch.bfloat16
+            self.c_dtype = torch.bfloat16  # recorded as the reference does; the activations keep their own dtype here
         self._preacts_natural_shape = (*group, reps)
         flat = self.p_dim == 2
         theta_shape = ((self.group_count, self._theta_natural_shape[-2] * self._theta_natural_shape[-1])
@@ -271,6 +287,9 @@ class QKANLayer(nn.Module):
         self._check_solver()
         if self.is_batchnorm:
             x = self.bn(x)
+        out_dtype = x.dtype
+        if self._io_bf16 and x.dtype != torch.bfloat16:
+            x = x.to(torch.bfloat16)  # c_dtype bfloat16 / float8: bf16 activations at the kernel boundary
         theta, pw, pb = self._kernel_params()
         use_pb = self.postact_bias_trainable or self._pb_is_nonzero
         mask = None if self._mask_is_identity else self._as_oi(self.mask)
@@ -287,7 +306,7 @@ class QKANLayer(nn.Module):
             # other base activations stay a plain library GEMM beside the kernel (qkan.py:755, 784)
             w = base_w if mask is None else base_w * mask
             y = y + F.linear(self.base_activation(x), w.to(x.dtype))
-        return y
+        return y if y.dtype == out_dtype else y.to(out_dtype)
 
     @torch.no_grad()
     def forward_no_sum(self, x: torch.Tensor) -> torch.Tensor:

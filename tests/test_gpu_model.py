@@ -381,3 +381,23 @@ def test_edge_statistics_at_transformer_width_use_no_batch_by_edge_tensor():
     gb = layer.edge_output_std(xb)
     wb = torch.std(sub.forward_no_sum(xb.float()), dim=0)
     assert nerr(gb[outs].float().cpu().numpy(), wb.cpu().numpy()) <= 1e-3
+
+
+@pytest.mark.parametrize("c_dtype", [torch.bfloat16, torch.float8_e4m3fn])
+def test_c_dtype_bfloat16_and_float8_run_with_bf16_activations(c_dtype):
+    """c_dtype=bfloat16 / float8_e4m3fn: activations cross the kernel boundary as bfloat16, parameters and the result
+    keep p_dtype, and values and gradients stay inside the bf16 bound of the float32 layer."""
+    kw = dict(reps=3, device="cuda", preact_trainable=True, postact_weight_trainable=True, seed=4)
+    ref, low = QKANLayer(24, 16, **kw), QKANLayer(24, 16, c_dtype=c_dtype, **kw)
+    x = (torch.rand(200, 24, device="cuda") * 2 - 1)
+    xr, xl = x.clone().requires_grad_(True), x.clone().requires_grad_(True)
+    gy = torch.randn(200, 16, device="cuda")
+    yr, yl = ref(xr), low(xl)
+    assert yl.dtype == torch.float32
+    (yr * gy).sum().backward()
+    (yl * gy).sum().backward()
+    assert nerr(yl.detach().cpu().numpy(), yr.detach().cpu().numpy()) <= TOL_BF16
+    assert nerr(xl.grad.cpu().numpy(), xr.grad.cpu().numpy()) <= TOL_BF16
+    for name in ("theta", "preacts_weight", "postact_weights"):
+        a, b = getattr(low, name).grad, getattr(ref, name).grad
+        assert a.dtype == torch.float32 and nerr(a.cpu().numpy(), b.cpu().numpy()) <= TOL_BF16, name

@@ -45,6 +45,30 @@ def test_constructor_signatures_match_the_reference_defaults():
     assert train["steps"].default == 10 and train["reg_metric"].default == "edge_forward_dr_n"
 
 
+def test_solver_default_differs_from_the_reference_on_purpose():
+    """The reference defaults to solver="exact" (its torch path, src/qkan/qkan.py:106-145); this package has one
+    solver and no CPU path, so its default is that solver, and any other name is refused when the layer runs."""
+    layer = inspect.signature(QKANLayer.__init__).parameters
+    model = inspect.signature(QKAN.__init__).parameters
+    assert layer["solver"].default == "b200" and model["solver"].default == "b200"
+    l = QKANLayer(3, 2, solver="exact")
+    with pytest.raises(NotImplementedError):
+        l(torch.zeros(4, 3))
+
+
+def test_c_dtype_values_the_reference_accepts():
+    """complex64/float32: float32 activations; bfloat16 and float8_e4m3fn: bfloat16 activations at the kernel
+    boundary (the fp8 value selects state-checkpoint storage in the reference, which this backward does not have);
+    anything else is refused instead of being passed through."""
+    assert QKANLayer(3, 2).c_dtype == torch.float32 and not QKANLayer(3, 2)._io_bf16
+    assert QKANLayer(3, 2, c_dtype=torch.complex128).c_dtype == torch.float64
+    assert QKANLayer(3, 2, c_dtype=torch.bfloat16)._io_bf16
+    assert QKANLayer(3, 2, c_dtype=torch.float8_e4m3fn)._io_bf16
+    assert QKANLayer(3, 2, ansatz="real").c_dtype == torch.bfloat16  # forced by the reference for this ansatz
+    with pytest.raises(ValueError):
+        QKANLayer(3, 2, c_dtype=torch.int8)
+
+
 def test_trainable_flags_follow_the_reference():
     l = QKANLayer(3, 2, preact_trainable=False, postact_weight_trainable=True, ba_trainable=False)
     assert not l.preacts_weight.requires_grad and not l.preacts_bias.requires_grad
