@@ -41,11 +41,15 @@ enum QkFlags {
     QK_PREACT_TRAINABLE = 1u, /* encode pw*x+pb; otherwise x itself (exact.py:87,121-124) */
     QK_FAST_MEASURE = 2u,     /* |a|-|b| readout; otherwise |a|^2-|b|^2 (torch_qc.py:261-277) */
     QK_USE_POSTACT_BIAS = 4u, /* add postact_bias before the weight (qkan.py:776-783) */
-    QK_PRECISE_MATH = 8u      /* sin/cos/sqrt by the full-precision routines instead of the special-function
+    QK_PRECISE_MATH = 8u,     /* sin/cos/sqrt by the full-precision routines instead of the special-function
                                  unit: ~1 ulp and smooth in the argument, as torch's own sin/cos in the
                                  reference are; meant for small fits driven by LBFGS. Honoured for QK_F32
                                  activations; with QK_BF16 activations the flag is accepted and has no effect
                                  (bfloat16 rounding of x and y is four orders of magnitude coarser) */
+    QK_SINGLE_TABLE = 16u     /* frozen preacts (QK_PREACT_TRAINABLE off): do not build the second per-edge table
+                                 that the angle-addition forward reads; the generic forward kernel runs instead
+                                 (about a fifth slower there) and qk_tables_bytes() is halved. For callers short
+                                 of scratch; qk_pz_forward_noalloc sets it by itself when that makes a layer fit */
 };
 
 enum QkError {

@@ -24,6 +24,7 @@ QK_PREACT_TRAINABLE = 1
 QK_FAST_MEASURE = 2
 QK_USE_POSTACT_BIAS = 4
 QK_PRECISE_MATH = 8
+QK_SINGLE_TABLE = 16
 
 (QK_DBG_BWD_GROUPS, QK_DBG_BWD_RPG, QK_DBG_BWD_RU, QK_DBG_BWD_OSPLIT, QK_DBG_NO_XTRIG, QK_DBG_VERBOSE,
  QK_DBG_FWD_THREADS, QK_DBG_FWD_TB, QK_DBG_FWD_OT) = range(9)

@@ -36,7 +36,7 @@ int check_desc(const QkDesc* d) {
     if (d->param_dtype != QK_F32 && d->param_dtype != QK_BF16)
         return fail(QK_ERR_BAD_ARGUMENT, "param_dtype %d is neither QK_F32 nor QK_BF16",
                     d->param_dtype);
-    if (d->flags & ~(QK_PREACT_TRAINABLE | QK_FAST_MEASURE | QK_USE_POSTACT_BIAS | QK_PRECISE_MATH))
+    if (d->flags & ~(QK_PREACT_TRAINABLE | QK_FAST_MEASURE | QK_USE_POSTACT_BIAS | QK_PRECISE_MATH | QK_SINGLE_TABLE))
         return fail(QK_ERR_BAD_ARGUMENT, "unknown flag bits 0x%x", d->flags);
     if (d->group < 0) return fail(QK_ERR_BAD_ARGUMENT, "group must be >= 0 (got %d)", d->group);
     if (d->group > 65535) return fail(QK_ERR_UNSUPPORTED, "group %d exceeds 65535", d->group);
@@ -51,7 +51,7 @@ int check_desc(const QkDesc* d) {
 // bound by issue slots, not by the special-function unit, so it keeps the generic kernel.)
 bool use_xtrig(const QkDesc& d) {
     const int rk = qk::compiled_reps(d.ansatz, d.reps);
-    return d.ansatz == QK_ANSATZ_PZ && !(d.flags & QK_PREACT_TRAINABLE) && !(d.flags & QK_PRECISE_MATH) &&
+    return d.ansatz == QK_ANSATZ_PZ && !(d.flags & (QK_PREACT_TRAINABLE | QK_PRECISE_MATH | QK_SINGLE_TABLE)) &&
            rk >= 1 && rk <= 8 && !qk::debug_get(qk::kDbgNoXtrig);
 }
 

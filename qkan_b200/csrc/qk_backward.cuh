@@ -20,6 +20,7 @@
 #include <type_traits>
 
 #include "qk_kernels.cuh"
+#include "qk_packed.cuh"
 
 namespace qk {
 
@@ -91,16 +92,23 @@ __device__ __forceinline__ float edge_backward(const EdgeFwd<R>& e, float x, flo
 
 constexpr int kGyChunk = 8;  // outputs whose grad_y columns are staged together
 
+// Two batch rows per instruction on the packed float32 operations (qk_packed.cuh): 1 = on (the special-function
+// variants with at least one repetition), 0 = the scalar form everywhere.
+#ifndef QK_PACKED_F32
+#define QK_PACKED_F32 1
+#endif
+
 // Register cap of the short circuits (up to 3 repetitions): two CTAs of 256 threads stay resident per SM and the
 // compiler spends the rest on scheduling; 4 to 8 repetitions are capped at 128 (still two CTAs: uncapped, the
 // 8-repetition kernel took 152 registers, lost its second CTA and a fifth of its speed); the padded 12- and
 // 16-repetition instantiations need more than that. The cap,
 // the block-size bound beside it and the inlining of the column sums are a measured optimum of the instruction
-// schedule, not limits the code needs. Backward call at 65536 x 256 -> 256, 3 repetitions (ms): cap 96 with the
-// block-size bound and inlined sums 14.95; without the bound 15.25; sums out of line 15.42; cap 88 15.46,
-// 104 15.32, 112 15.00, 128 15.53.
+// schedule, not limits the code needs. Backward call at 65536 x 256 -> 256, 3 repetitions (ms), scalar form: cap 96
+// with the block-size bound and inlined sums 14.95; without the bound 15.25; sums out of line 15.42; cap 88 15.46,
+// 104 15.32, 112 15.00, 128 15.53. Packed form (two rows per instruction): cap 80 14.92, 96 14.50, 112 14.29,
+// 128 14.40.
 #ifndef QK_BWD_SHORT_MAXNREG
-#define QK_BWD_SHORT_MAXNREG 96
+#define QK_BWD_SHORT_MAXNREG 112
 #endif
 #ifdef QK_BWD_COLSUM_NOINLINE
 #define QK_COLSUM_LINKAGE static __device__ __noinline__
@@ -195,48 +203,94 @@ __global__ void __launch_bounds__(256) __maxnreg__(R <= 3 ? QK_BWD_SHORT_MAXNREG
             EdgeFwd<R> e;
             e.load(a.table + ((size_t)o * a.ipad + i) * KS);
             float acc[NACC];
-#pragma unroll
-            for (int k = 0; k < NACC; ++k) acc[k] = 0.f;
-
+            // (from 7 repetitions on, the constants as register pairs no longer fit beside two resident CTAs)
+            constexpr bool kPacked = QK_PACKED_F32 != 0 && !PRECISE && R >= 1 && R <= 6 && (RU % 2) == 0;
             const float* gyp = gy_s + ol * tb + row0;
             float* p = my;
-#pragma unroll 1
-            for (int j = 0; j < rpg; j += RU, p += RU * ROW) {
-                float xv[RU], gxo[RU], g[RU];
+            if constexpr (kPacked) {
+                EdgePk<R> e2;
+                e2.from(e);
+                f2 acc2[NACC];
 #pragma unroll
-                for (int u = 0; u < RU; ++u) {
-                    const float2 xg = *reinterpret_cast<const float2*>(p + u * ROW);
-                    xv[u] = xg.x;
-                    gxo[u] = xg.y;
-                    if (EDGES) {
-                        const int b = b0 + row0 + j + u;
-                        g[u] = 0.f;
-                        if (b < a.batch && i < a.in_dim)
-                            g[u] = ld_as_float(gsrc + ((size_t)b * a.out_dim + o) * a.in_dim + i);
-                    } else if (RU != 2 && RU != 4) {
-                        g[u] = gyp[j + u];
+                for (int k = 0; k < NACC; ++k) acc2[k] = pk(0.f);
+#pragma unroll 1
+                for (int j = 0; j < rpg; j += RU, p += RU * ROW) {
+                    float xv[RU], gxo[RU], g[RU];
+#pragma unroll
+                    for (int u = 0; u < RU; ++u) {
+                        const float2 xg = *reinterpret_cast<const float2*>(p + u * ROW);
+                        xv[u] = xg.x;
+                        gxo[u] = xg.y;
+                        if (EDGES) {
+                            const int b = b0 + row0 + j + u;
+                            g[u] = 0.f;
+                            if (b < a.batch && i < a.in_dim)
+                                g[u] = ld_as_float(gsrc + ((size_t)b * a.out_dim + o) * a.in_dim + i);
+                        }
+                    }
+                    if (!EDGES && RU == 2) {
+                        const float2 gv = *reinterpret_cast<const float2*>(gyp + j);
+                        g[0] = gv.x;
+                        g[RU - 1] = gv.y;
+                    }
+                    if (!EDGES && RU == 4) {
+                        const float4 gv = *reinterpret_cast<const float4*>(gyp + j);
+                        g[0] = gv.x;
+                        g[1 % RU] = gv.y;
+                        g[2 % RU] = gv.z;
+                        g[3 % RU] = gv.w;
+                    }
+#pragma unroll
+                    for (int u = 0; u < RU; u += 2) {
+                        const f2 gx2 = edge_backward2<R, FAST, EDGES, NACC>(
+                            e2, make_float2(xv[u], xv[u + 1]), make_float2(g[u], g[u + 1]),
+                            make_float2(gxo[u], gxo[u + 1]), acc2);
+                        p[u * ROW + 1] = gx2.x;
+                        p[(u + 1) * ROW + 1] = gx2.y;
                     }
                 }
-                // tb, row0 and j are multiples of RU, so the staged grad_y values of these rows
-                // are one aligned vector (same address in every lane: a broadcast load)
-                if (!EDGES && RU == 2) {
-                    const float2 gv = *reinterpret_cast<const float2*>(gyp + j);
-                    g[0] = gv.x;
-                    g[RU - 1] = gv.y;
-                }
-                if (!EDGES && RU == 4) {
-                    const float4 gv = *reinterpret_cast<const float4*>(gyp + j);
-                    g[0] = gv.x;
-                    g[1 % RU] = gv.y;
-                    g[2 % RU] = gv.z;
-                    g[3 % RU] = gv.w;
-                }
 #pragma unroll
-                for (int u = 0; u < RU; ++u) {
-                    p[u * ROW + 1] = edge_backward<R, FAST, EDGES, NACC, PRECISE>(e, xv[u], g[u], gxo[u], acc);
+                for (int k = 0; k < NACC; ++k) acc[k] = acc2[k].x + acc2[k].y;
+            } else {
+#pragma unroll
+                for (int k = 0; k < NACC; ++k) acc[k] = 0.f;
+#pragma unroll 1
+                for (int j = 0; j < rpg; j += RU, p += RU * ROW) {
+                    float xv[RU], gxo[RU], g[RU];
+#pragma unroll
+                    for (int u = 0; u < RU; ++u) {
+                        const float2 xg = *reinterpret_cast<const float2*>(p + u * ROW);
+                        xv[u] = xg.x;
+                        gxo[u] = xg.y;
+                        if (EDGES) {
+                            const int b = b0 + row0 + j + u;
+                            g[u] = 0.f;
+                            if (b < a.batch && i < a.in_dim)
+                                g[u] = ld_as_float(gsrc + ((size_t)b * a.out_dim + o) * a.in_dim + i);
+                        } else if (RU != 2 && RU != 4) {
+                            g[u] = gyp[j + u];
+                        }
+                    }
+                    // tb, row0 and j are multiples of RU, so the staged grad_y values of these rows
+                    // are one aligned vector (same address in every lane: a broadcast load)
+                    if (!EDGES && RU == 2) {
+                        const float2 gv = *reinterpret_cast<const float2*>(gyp + j);
+                        g[0] = gv.x;
+                        g[RU - 1] = gv.y;
+                    }
+                    if (!EDGES && RU == 4) {
+                        const float4 gv = *reinterpret_cast<const float4*>(gyp + j);
+                        g[0] = gv.x;
+                        g[1 % RU] = gv.y;
+                        g[2 % RU] = gv.z;
+                        g[3 % RU] = gv.w;
+                    }
+#pragma unroll
+                    for (int u = 0; u < RU; ++u) {
+                        p[u * ROW + 1] = edge_backward<R, FAST, EDGES, NACC, PRECISE>(e, xv[u], g[u], gxo[u], acc);
+                    }
                 }
             }
-
             // block-level reduction over the row groups, then this tile's partial
             float* red = red_s + (size_t)(o & 1) * groups * NACC * 32;
 #pragma unroll

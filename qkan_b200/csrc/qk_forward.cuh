@@ -12,6 +12,7 @@
 #include <type_traits>
 
 #include "qk_kernels.cuh"
+#include "qk_packed.cuh"
 
 namespace qk {
 
@@ -33,15 +34,20 @@ __device__ __forceinline__ float transpose_reduce32(float (&v)[32], int lane) {
 
 __device__ __forceinline__ float silu_f(float v) { return v / (1.f + expf(-v)); }
 
-// One row in QK_FWD_POLY_EVERY of a lane's 32-row block evaluates the sin/cos of its first QK_FWD_POLY_GATES data
-// gates on the FMA pipe (poly_sincos) instead of the special-function unit, which bounds this kernel; 0 switches
-// that off. Measured at 65536 x 256 -> 256, 3 repetitions (forward, ms): off 8.72; one gate of every 4th row 8.57,
+// One row pair in QK_FWD_POLY_EVERY of a lane's 32-row block (one row, in the scalar form) evaluates the sin/cos of
+// its first QK_FWD_POLY_GATES data gates on the FMA pipe (poly_sincos) instead of the special-function unit, which
+// bounds this kernel; 0 switches that off. Packed form (two rows per instruction), forward ms at 65536 x 256 -> 256,
+// 3 repetitions: off 8.37; one gate of every pair 8.07 (kept), of every 2nd pair 8.19, of every 4th 8.34; two gates
+// of every pair 9.56, of every 2nd 8.59; all three of every 3rd 8.59. Scalar form: Measured at 65536 x 256 -> 256, 3 repetitions (forward, ms): off 8.72; one gate of every 4th row 8.57,
 // of every 3rd 8.66, of every 2nd 8.61, of every row 9.12; two gates of every 4th row 8.58, of every 2nd 9.14;
 // all gates of every 8th row 8.66, of every 6th 8.72, of every 4th 8.86, of every 3rd 9.06. The unit is 84 % busy
 // without it, yet moving more than a twelfth of the calls off it loses again: the kernel is as much bound by
 // its queue to that unit, which the shuffles and shared-memory reads share, as by the unit itself.
+#ifndef QK_PACKED_F32
+#define QK_PACKED_F32 1
+#endif
 #ifndef QK_FWD_POLY_EVERY
-#define QK_FWD_POLY_EVERY 4
+#define QK_FWD_POLY_EVERY 1
 #endif
 #ifndef QK_FWD_POLY_GATES
 #define QK_FWD_POLY_GATES 1
@@ -101,8 +107,51 @@ __global__ void QK_FWD_REGCAP forward_kernel(FwdArgs a) {
                 EdgeFwd<R> e;
                 e.load(a.table + ((size_t)o * a.ipad + i) * KS);
                 const float bw = e.bw;
+                // (the frozen-preact form measured slower packed: 8.58 against 7.33 ms, so it stays scalar)
+                constexpr bool kPacked = QK_PACKED_F32 != 0 && !PRECISE && !XTRIG && R >= 1 && R <= 12;
+                constexpr int kPolyGates = R < QK_FWD_POLY_GATES ? R : QK_FWD_POLY_GATES;
+                constexpr int kEvery = QK_FWD_POLY_EVERY > 0 ? QK_FWD_POLY_EVERY : 1;
+                EdgePk<R> e2;
+                f2 nc2[R > 0 ? R : 1];
+                if constexpr (kPacked) {
+                    e2.from(e);
+                    if constexpr (XTRIG) {
+#pragma unroll
+                        for (int l = 0; l < R; ++l) nc2[l] = pk(-e.c[l]);
+                    }
+                }
                 for (int rg = 0; rg < tb; rg += 32) {
                     float v[32];
+                    if constexpr (kPacked) {
+                        // two rows per instruction (qk_packed.cuh); pair q = r / 2 takes its first kPolyGates data
+                        // gates from the polynomial when q % kEvery == kEvery - 1
+#pragma unroll
+                        for (int r = 0; r < 32; r += 2) {
+                            f2 p2;
+                            if constexpr (XTRIG) {
+                                const float2 t0 = reinterpret_cast<const float2*>(x_s)[(rg + r) * ich + col];
+                                const float2 t1 = reinterpret_cast<const float2*>(x_s)[(rg + r + 1) * ich + col];
+                                p2 = edge_forward_xtrig2<R, FAST>(e2, nc2, make_float2(t0.x, t1.x), make_float2(t0.y, t1.y));
+                            } else {
+                                const f2 x2 = make_float2(x_s[(rg + r) * ich + col], x_s[(rg + r + 1) * ich + col]);
+                                f2 vx, vy, vz, ir, rr;
+                                if (QK_FWD_POLY_EVERY > 0 && ((r / 2) % kEvery) == kEvery - 1)
+                                    p2 = edge_forward2<R, FAST, false, kPolyGates>(e2, x2, nullptr, nullptr, nullptr, vx, vy, vz, ir, rr);
+                                else
+                                    p2 = edge_forward2<R, FAST, false, 0>(e2, x2, nullptr, nullptr, nullptr, vx, vy, vz, ir, rr);
+                            }
+                            if (EDGES) {
+                                v[r] = p2.x;
+                                v[r + 1] = p2.y;
+                            } else {
+                                f2 val = mul2(p2, e2.w);
+                                if (BASE)
+                                    val = fma2(make_float2(b_s[(rg + r) * ich + col], b_s[(rg + r + 1) * ich + col]), pk(bw), val);
+                                v[r] = val.x;
+                                v[r + 1] = val.y;
+                            }
+                        }
+                    } else {
 #pragma unroll
                     for (int r = 0; r < 32; ++r) {
                         float p;
@@ -125,6 +174,7 @@ __global__ void QK_FWD_REGCAP forward_kernel(FwdArgs a) {
                             if (BASE) val = fmaf(b_s[(rg + r) * ich + col], bw, val);
                             v[r] = val;
                         }
+                    }
                     }
                     if (EDGES) {
                         IO* out = static_cast<IO*>(a.postacts);

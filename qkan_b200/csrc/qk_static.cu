@@ -41,7 +41,7 @@ int qk_pz_forward_noalloc(const QkDesc* desc, const void* x, const float* theta,
                           const void* postact_weights, const void* postact_bias,
                           const void* base_weight, const void* mask, void* y, void* cuda_stream) {
     g_static_err[0] = 0;
-    const size_t need = qk_forward_workspace_bytes(desc);
+    size_t need = qk_forward_workspace_bytes(desc);
     if (need == 0) {
         // the descriptor itself was rejected: let the regular entry point name the reason, so that both entry
         // points answer a bad or unsupported descriptor with the same code (it fails before touching memory)
@@ -49,6 +49,16 @@ int qk_pz_forward_noalloc(const QkDesc* desc, const void* x, const float* theta,
                                      postact_bias, base_weight, mask, y, nullptr, 0, cuda_stream);
         snprintf(g_static_err, sizeof(g_static_err), "%s", qk_last_error());
         return rc != QK_OK ? rc : QK_ERR_BAD_ARGUMENT;
+    }
+    QkDesc single = *desc;
+    if (need > kStaticScratchBytes) {
+        // a frozen-preact layer keeps two tables; with one (and the generic forward kernel) it may still fit
+        single.flags |= QK_SINGLE_TABLE;
+        const size_t need_single = qk_forward_workspace_bytes(&single);
+        if (need_single != 0 && need_single <= kStaticScratchBytes) {
+            desc = &single;
+            need = need_single;
+        }
     }
     if (need > kStaticScratchBytes) {
         snprintf(g_static_err, sizeof(g_static_err),

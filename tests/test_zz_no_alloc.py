@@ -84,6 +84,20 @@ def test_noalloc_forward_frozen_preacts_and_bf16_activations():
     assert nerr(yb, _oracle_y(p, flags | _abi.QK_PREACT_TRAINABLE)) <= TOL_BF16
 
 
+def test_noalloc_keeps_its_capacity_for_frozen_preacts():
+    """256 x 256 at 3 repetitions with frozen preacts: the two-table form needs 10.5 MB, more than the built-in
+    8 MiB, so the entry point runs the one-table form by itself; same results within the float32 bound."""
+    from qkan_b200 import _abi
+
+    lib = _abi.load()
+    flags = _abi.QK_FAST_MEASURE | _abi.QK_USE_POSTACT_BIAS
+    desc = _abi.QkDesc(48, 256, 256, 3, _abi.QK_F32, _abi.QK_F32, flags, 0)
+    assert lib.qk_forward_workspace_bytes(_abi.desc_pointer(desc)) > lib.qk_noalloc_max_scratch_bytes()
+    p = random_problem(63, 48, 256, 256, 3, use_pb=True)
+    y, y_ref = _call_both(p, flags)
+    assert nerr(y, y_ref) <= TOL_F32 and nerr(y, _oracle_y(p, flags)) <= TOL_F32
+
+
 def test_noalloc_forward_on_a_second_device():
     """Each GPU has its own copy of the built-in array and its own looked-up address."""
     if torch.cuda.device_count() < 2:
