@@ -25,15 +25,15 @@
 namespace qk {
 
 // Returns gx0 + d/dx of this edge (gx0 is the grad_x accumulated over the outputs walked so far).
-template <int R, bool FAST, bool EDGES, int NACC, bool PRECISE>
-__device__ __forceinline__ float edge_backward(const EdgeFwd<R>& e, float x, float g, float gx0,
-                                               float (&acc)[NACC]) {
+// `acc(k)` is a reference to accumulator k (a float array, or one half of a packed pair).
+template <int R, bool FAST, bool EDGES, bool PRECISE, class Acc>
+__device__ __forceinline__ float edge_backward_to(const EdgeFwd<R>& e, float x, float g, float gx0, Acc acc) {
     if constexpr (R == 0) {
-        // "real" ansatz: p = f(alpha), alpha = A x + C. acc[0] = sum dL/dalpha, acc[1] = sum dL/dalpha * x
+        // "real" ansatz: p = f(alpha), alpha = A x + C. acc(0) = sum dL/dalpha, acc(1) = sum dL/dalpha * x
         float s, c, r = 1.f;
         const float p = real_forward<FAST, PRECISE>(e, x, s, c, r);
         const float gp = EDGES ? g : g * e.w;
-        if (!EDGES) acc[a_w(0)] = fmaf(g, p, acc[a_w(0)]);
+        if (!EDGES) acc(a_w(0)) = fmaf(g, p, acc(a_w(0)));
         float dp = -s;
         if (FAST) {
             // d/dalpha [cos * (1+|sin|)^(-1/2)] = -sin r - (1/2) cos^2 r^3 sign(sin)
@@ -41,14 +41,14 @@ __device__ __forceinline__ float edge_backward(const EdgeFwd<R>& e, float x, flo
             dp = -fmaf((0.5f * c) * c, (r * r) * (r * sgn), s * r);
         }
         const float ga = gp * dp;
-        acc[0] += ga;
-        acc[1] = fmaf(ga, x, acc[1]);
+        acc(0) += ga;
+        acc(1) = fmaf(ga, x, acc(1));
         return fmaf(ga, e.a, gx0);
     } else {
     float cs[R], sn[R], vx, vy, vz, inv_rho, r;
     const float p = edge_forward<R, FAST, true, PRECISE>(e, x, cs, sn, vx, vy, vz, inv_rho, r);
     const float gp = EDGES ? g : g * e.w;
-    if (!EDGES) acc[a_w(R)] = fmaf(g, p, acc[a_w(R)]);
+    if (!EDGES) acc(a_w(R)) = fmaf(g, p, acc(a_w(R)));
     // w = v x a, a = cotangent of the final Bloch vector (its z component of w is 0)
     float wx, wy, wz;
     if (FAST) {
@@ -61,21 +61,21 @@ __device__ __forceinline__ float edge_backward(const EdgeFwd<R>& e, float x, flo
         wx = vy * gp;
         wy = -(vx * gp);
     }
-    acc[a_ry(R)] += wy;  // final Ry(theta[R,1])
+    acc(a_ry(R)) += wy;  // final Ry(theta[R,1])
     wz = wx * e.sf;
     wx = wx * e.cf;
     float gx = gx0;
 #pragma unroll
     for (int l = R - 1; l >= 0; --l) {
         // merged Rz(pw_l x + c_l): its angle gradient is wz
-        acc[a_c(R, l)] += wz;
-        acc[a_pwx(R, l)] = fmaf(wz, x, acc[a_pwx(R, l)]);
+        acc(a_c(R, l)) += wz;
+        acc(a_pwx(R, l)) = fmaf(wz, x, acc(a_pwx(R, l)));
         gx = fmaf(wz, e.pw[l], gx);
         float nx = fmaf(wy, sn[l], wx * cs[l]);
         float ny = fmaf(-wx, sn[l], wy * cs[l]);
         wx = nx;
         wy = ny;
-        acc[a_ry(l)] += wy;  // Ry(theta[l,1])
+        acc(a_ry(l)) += wy;  // Ry(theta[l,1])
         if (l > 0) {
             float mx = fmaf(-wz, e.sa[l], wx * e.ca[l]);
             float mz = fmaf(wx, e.sa[l], wz * e.ca[l]);
@@ -85,9 +85,15 @@ __device__ __forceinline__ float edge_backward(const EdgeFwd<R>& e, float x, flo
             wz = fmaf(wx, e.sa[0], wz * e.ca[0]);
         }
     }
-    acc[a_t00(R)] += wz;  // Rz(theta[0,0])
+    acc(a_t00(R)) += wz;  // Rz(theta[0,0])
     return gx;
     }
+}
+
+template <int R, bool FAST, bool EDGES, int NACC, bool PRECISE>
+__device__ __forceinline__ float edge_backward(const EdgeFwd<R>& e, float x, float g, float gx0,
+                                               float (&acc)[NACC]) {
+    return edge_backward_to<R, FAST, EDGES, PRECISE>(e, x, g, gx0, [&](int k) -> float& { return acc[k]; });
 }
 
 constexpr int kGyChunk = 8;  // outputs whose grad_y columns are staged together
@@ -96,6 +102,13 @@ constexpr int kGyChunk = 8;  // outputs whose grad_y columns are staged together
 // variants with at least one repetition), 0 = the scalar form everywhere.
 #ifndef QK_PACKED_F32
 #define QK_PACKED_F32 1
+#endif
+// With four rows in flight: 1 = rows 0,1 as a packed pair and rows 2,3 as scalar rows, 0 = two packed pairs.
+// The counters show the packed operations on one half of the FMA pipe only, so scalar rows were tried for the
+// other half: measured slower (backward call 14.82 ms against 14.30 at the headline shape; 14.87 / 15.29 with
+// register caps 128 / 96), so it stays off.
+#ifndef QK_BWD_HYBRID
+#define QK_BWD_HYBRID 0
 #endif
 
 // Register cap of the short circuits (up to 3 repetitions): two CTAs of 256 threads stay resident per SM and the
@@ -242,6 +255,13 @@ __global__ void __launch_bounds__(256) __maxnreg__(R <= 3 ? QK_BWD_SHORT_MAXNREG
                     }
 #pragma unroll
                     for (int u = 0; u < RU; u += 2) {
+                        if (QK_BWD_HYBRID != 0 && RU == 4 && u == 2) {
+                            p[u * ROW + 1] = edge_backward_to<R, FAST, EDGES, false>(
+                                e, xv[u], g[u], gxo[u], [&](int k) -> float& { return acc2[k].x; });
+                            p[(u + 1) * ROW + 1] = edge_backward_to<R, FAST, EDGES, false>(
+                                e, xv[u + 1], g[u + 1], gxo[u + 1], [&](int k) -> float& { return acc2[k].y; });
+                            continue;
+                        }
                         const f2 gx2 = edge_backward2<R, FAST, EDGES, NACC>(
                             e2, make_float2(xv[u], xv[u + 1]), make_float2(g[u], g[u + 1]),
                             make_float2(gxo[u], gxo[u + 1]), acc2);

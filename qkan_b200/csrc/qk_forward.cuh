@@ -49,6 +49,11 @@ __device__ __forceinline__ float silu_f(float v) { return v / (1.f + expf(-v)); 
 #ifndef QK_FWD_POLY_EVERY
 #define QK_FWD_POLY_EVERY 1
 #endif
+// One row pair in QK_FWD_SCALAR_EVERY is evaluated as two scalar rows; 0 = every pair packed. Measured at the
+// headline shape (forward, ms): 0: 8.05; every 4th 8.09, every 3rd 8.17, every 2nd 8.30: mixing does not pay.
+#ifndef QK_FWD_SCALAR_EVERY
+#define QK_FWD_SCALAR_EVERY 0
+#endif
 #ifndef QK_FWD_POLY_GATES
 #define QK_FWD_POLY_GATES 1
 #endif
@@ -134,11 +139,18 @@ __global__ void QK_FWD_REGCAP forward_kernel(FwdArgs a) {
                                 p2 = edge_forward_xtrig2<R, FAST>(e2, nc2, make_float2(t0.x, t1.x), make_float2(t0.y, t1.y));
                             } else {
                                 const f2 x2 = make_float2(x_s[(rg + r) * ich + col], x_s[(rg + r + 1) * ich + col]);
+                                constexpr int kScalarEvery = QK_FWD_SCALAR_EVERY > 0 ? QK_FWD_SCALAR_EVERY : 1;
+                                if (QK_FWD_SCALAR_EVERY > 0 && ((r / 2) % kScalarEvery) == kScalarEvery - 1) {
+                                    float sx, sy, sz, si, sr;
+                                    p2.x = edge_forward<R, FAST, false, false>(e, x2.x, nullptr, nullptr, sx, sy, sz, si, sr);
+                                    p2.y = edge_forward<R, FAST, false, false>(e, x2.y, nullptr, nullptr, sx, sy, sz, si, sr);
+                                } else {
                                 f2 vx, vy, vz, ir, rr;
                                 if (QK_FWD_POLY_EVERY > 0 && ((r / 2) % kEvery) == kEvery - 1)
                                     p2 = edge_forward2<R, FAST, false, kPolyGates>(e2, x2, nullptr, nullptr, nullptr, vx, vy, vz, ir, rr);
                                 else
                                     p2 = edge_forward2<R, FAST, false, 0>(e2, x2, nullptr, nullptr, nullptr, vx, vy, vz, ir, rr);
+                                }
                             }
                             if (EDGES) {
                                 v[r] = p2.x;

@@ -178,7 +178,8 @@ class OverlappedGradSync:
     """
 
     def __init__(self, module: torch.nn.Module, groups: Optional[list] = None,
-                 group: Optional[dist.ProcessGroup] = None, average: bool = True):
+                 group: Optional[dist.ProcessGroup] = None, average: bool = True,
+                 min_bucket_bytes: int = 1 << 20):
         if groups is None:
             children = list(getattr(module, "layers", module).children()) or [module]
             groups = [[p for p in c.parameters() if p.requires_grad] for c in children]
@@ -186,8 +187,20 @@ class OverlappedGradSync:
             rest = [p for p in module.parameters() if p.requires_grad and id(p) not in seen]
             if rest:
                 groups.append(rest)
-        self.groups = [g for g in groups if g]
+        # neighbouring layers whose gradients are small share a bucket: below about a megabyte a collective is all
+        # latency, and one launch for two layers beats two
+        merged: list = []
+        for g in (g for g in groups if g):
+            if merged and sum(p.numel() for p in merged[-1]) * 4 < min_bucket_bytes:
+                merged[-1] = merged[-1] + list(g)
+            else:
+                merged.append(list(g))
+        self.groups = merged
         self.pg, self.average = group, average
+        # NCCL averages inside the collective; other backends (gloo in the CPU tests) sum, and finish() divides
+        self._avg_in_collective = False
+        if average and dist.is_available() and dist.is_initialized():
+            self._avg_in_collective = dist.get_backend(group) == "nccl"
         self.flats, self._pending, self._handles, self._hooks = [], [], [], []
         for gi, params in enumerate(self.groups):
             dev = params[0].device
@@ -217,7 +230,8 @@ class OverlappedGradSync:
 
     def _launch(self, gi: int) -> None:
         if dist.is_available() and dist.is_initialized() and dist.get_world_size(self.pg) > 1:
-            self._handles.append(dist.all_reduce(self.flats[gi], op=dist.ReduceOp.SUM, group=self.pg, async_op=True))
+            op = dist.ReduceOp.AVG if self._avg_in_collective else dist.ReduceOp.SUM
+            self._handles.append(dist.all_reduce(self.flats[gi], op=op, group=self.pg, async_op=True))
 
     def zero_grad(self) -> None:
         """Clear the buckets, re-attach the views and arm the ready counters for the next backward."""
@@ -237,7 +251,7 @@ class OverlappedGradSync:
         for h in self._handles:
             h.wait()
         self._handles = []
-        if self.average and dist.is_available() and dist.is_initialized():
+        if self.average and not self._avg_in_collective and dist.is_available() and dist.is_initialized():
             world = dist.get_world_size(self.pg)
             if world > 1:
                 for flat in self.flats:

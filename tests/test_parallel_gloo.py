@@ -124,8 +124,11 @@ def _overlap_worker(rank: int, world: int, port: int, out):
         torch.nn.functional.mse_loss(model(full_x), full_t).backward()
         want = [p.grad.clone() for p in model.parameters()]
         model.zero_grad(set_to_none=True)
-        sync = OverlappedGradSync(model)
-        ok = len(sync.groups) == 3
+        merged = OverlappedGradSync(model)  # small layers share a bucket
+        ok = len(merged.groups) == 1
+        merged.remove()
+        sync = OverlappedGradSync(model, min_bucket_bytes=0)
+        ok = ok and len(sync.groups) == 3
         b, e = shard_rows(12, rank, world)
         for _ in range(2):  # twice: the buckets are cleared and re-armed by zero_grad()
             sync.zero_grad()
