@@ -9,6 +9,7 @@
 // at a time and read back as 128-bit broadcasts, and the batch sum of grad_base_weight is reduced over the
 // warps in shared memory and written as one partial per (row tile, output) for finish_grads.
 #include "qk_kernels.cuh"
+#include "qk_packed.cuh"
 
 namespace qk {
 
@@ -72,19 +73,24 @@ __global__ void __launch_bounds__(kBaseWarps * kWarp, 3) base_backward_kernel(Ba
 #pragma unroll 2
         for (int c = 0; c < kBaseChunk; ++c) {
             const float bw = bw_s[buf][c][lane];
-            float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;  // four independent chains for the batch sum
+            // two rows per instruction on the packed float32 operations: the staged grad_y vector and the thread's
+            // silu(x) / grad_x registers are natural row pairs; two independent chains for the batch sum
+            const f2 bw2 = pk(bw);
+            f2 sa = pk(0.f), sb = pk(0.f);
 #pragma unroll
             for (int r = 0; r < RPW; r += 4) {
                 const float4 g = *reinterpret_cast<const float4*>(&gy_s[buf][c][row0 + r]);
-                gxb[r] = fmaf(g.x, bw, gxb[r]);
-                gxb[r + 1] = fmaf(g.y, bw, gxb[r + 1]);
-                gxb[r + 2] = fmaf(g.z, bw, gxb[r + 2]);
-                gxb[r + 3] = fmaf(g.w, bw, gxb[r + 3]);
-                s0 = fmaf(g.x, sl[r], s0);
-                s1 = fmaf(g.y, sl[r + 1], s1);
-                s2 = fmaf(g.z, sl[r + 2], s2);
-                s3 = fmaf(g.w, sl[r + 3], s3);
+                const f2 g01 = make_float2(g.x, g.y), g23 = make_float2(g.z, g.w);
+                const f2 a01 = fma2(g01, bw2, make_float2(gxb[r], gxb[r + 1]));
+                const f2 a23 = fma2(g23, bw2, make_float2(gxb[r + 2], gxb[r + 3]));
+                gxb[r] = a01.x;
+                gxb[r + 1] = a01.y;
+                gxb[r + 2] = a23.x;
+                gxb[r + 3] = a23.y;
+                sa = fma2(g01, make_float2(sl[r], sl[r + 1]), sa);
+                sb = fma2(g23, make_float2(sl[r + 2], sl[r + 3]), sb);
             }
+            const float s0 = sa.x, s1 = sa.y, s2 = sb.x, s3 = sb.y;
             // written after this chunk's staging barrier, i.e. after the last chunk's reads
             red_s[w][c][lane] = (s0 + s1) + (s2 + s3);
         }
