@@ -49,6 +49,9 @@ __device__ __forceinline__ float silu_f(float v) { return v / (1.f + expf(-v)); 
 #ifndef QK_FWD_POLY_EVERY
 #define QK_FWD_POLY_EVERY 1
 #endif
+#ifndef QK_XTRIG_PACKED
+#define QK_XTRIG_PACKED 0
+#endif
 // One row pair in QK_FWD_SCALAR_EVERY is evaluated as two scalar rows; 0 = every pair packed. Measured at the
 // headline shape (forward, ms): 0: 8.05; every 4th 8.09, every 3rd 8.17, every 2nd 8.30: mixing does not pay.
 #ifndef QK_FWD_SCALAR_EVERY
@@ -112,19 +115,13 @@ __global__ void QK_FWD_REGCAP forward_kernel(FwdArgs a) {
                 EdgeFwd<R> e;
                 e.load(a.table + ((size_t)o * a.ipad + i) * KS);
                 const float bw = e.bw;
-                // (the frozen-preact form measured slower packed: 8.58 against 7.33 ms, so it stays scalar)
-                constexpr bool kPacked = QK_PACKED_F32 != 0 && !PRECISE && !XTRIG && R >= 1 && R <= 12;
+                // (the frozen-preact form gains nothing from packing, 7.31 against 7.32 ms: it is all FMA-pipe work, which the
+                // packed operations do not speed up; QK_XTRIG_PACKED = 1 selects it anyway)
+                constexpr bool kPacked = QK_PACKED_F32 != 0 && !PRECISE && (!XTRIG || QK_XTRIG_PACKED != 0) && R >= 1 && R <= 12;
                 constexpr int kPolyGates = R < QK_FWD_POLY_GATES ? R : QK_FWD_POLY_GATES;
                 constexpr int kEvery = QK_FWD_POLY_EVERY > 0 ? QK_FWD_POLY_EVERY : 1;
                 EdgePk<R> e2;
-                f2 nc2[R > 0 ? R : 1];
-                if constexpr (kPacked) {
-                    e2.from(e);
-                    if constexpr (XTRIG) {
-#pragma unroll
-                        for (int l = 0; l < R; ++l) nc2[l] = pk(-e.c[l]);
-                    }
-                }
+                if constexpr (kPacked) e2.from(e);
                 for (int rg = 0; rg < tb; rg += 32) {
                     float v[32];
                     if constexpr (kPacked) {
@@ -136,7 +133,7 @@ __global__ void QK_FWD_REGCAP forward_kernel(FwdArgs a) {
                             if constexpr (XTRIG) {
                                 const float2 t0 = reinterpret_cast<const float2*>(x_s)[(rg + r) * ich + col];
                                 const float2 t1 = reinterpret_cast<const float2*>(x_s)[(rg + r + 1) * ich + col];
-                                p2 = edge_forward_xtrig2<R, FAST>(e2, nc2, make_float2(t0.x, t1.x), make_float2(t0.y, t1.y));
+                                p2 = edge_forward_xtrig2<R, FAST>(e2, make_float2(t0.x, t1.x), make_float2(t0.y, t1.y));
                             } else {
                                 const f2 x2 = make_float2(x_s[(rg + r) * ich + col], x_s[(rg + r + 1) * ich + col]);
                                 constexpr int kScalarEvery = QK_FWD_SCALAR_EVERY > 0 ? QK_FWD_SCALAR_EVERY : 1;

@@ -77,3 +77,58 @@ def test_two_rank_data_parallel_matches_single_gpu():
     for rank_result in results:  # every rank ends with the same, full-batch parameter gradients
         for k, v in rank_result[3].items():
             assert nerr(v, g_ref[k].cpu().numpy()) <= 2e-6, k
+
+
+def _model_worker(rank: int, world: int, port: int, out):
+    """Two-layer model, per-layer gradient buckets reduced under the backward (NCCL, averaged in the collective)."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank),
+                      LOCAL_RANK=str(rank), WORLD_SIZE=str(world), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from qkan_b200 import QKAN
+        from qkan_b200.parallel import OverlappedGradSync, shard_rows
+
+        model = QKAN([24, 16, 5], reps=2, device=dev, seed=3, preact_trainable=True, ba_trainable=True)
+        sync = OverlappedGradSync(model, min_bucket_bytes=0)
+        g = torch.Generator().manual_seed(11)
+        x = torch.rand(128, 24, generator=g).to(dev)
+        t = torch.rand(128, 5, generator=g).to(dev)
+        b, e = shard_rows(128, rank, world)
+        for _ in range(2):  # the second pass reuses cleared, re-armed buckets
+            sync.zero_grad()
+            torch.nn.functional.mse_loss(model(x[b:e]), t[b:e]).backward()
+            sync.finish()
+        torch.cuda.synchronize()
+        out.put((rank, len(sync.groups), {n: p.grad.cpu().numpy() for n, p in model.named_parameters()
+                                          if p.grad is not None}))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_rank_overlapped_layer_buckets_match_single_gpu():
+    from qkan_b200 import QKAN
+
+    model = QKAN([24, 16, 5], reps=2, device="cuda", seed=3, preact_trainable=True, ba_trainable=True)
+    g = torch.Generator().manual_seed(11)
+    x = torch.rand(128, 24, generator=g).cuda()
+    t = torch.rand(128, 5, generator=g).cuda()
+    torch.nn.functional.mse_loss(model(x), t).backward()
+    want = {n: p.grad.cpu().numpy() for n, p in model.named_parameters() if p.grad is not None}
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_model_worker, args=(r, 2, port, out)) for r in range(2)]
+    for pr in procs:
+        pr.start()
+    results = sorted((out.get(timeout=180) for _ in procs), key=lambda r: r[0])
+    for pr in procs:
+        pr.join(timeout=60)
+        assert pr.exitcode == 0
+    for _, n_groups, grads in results:
+        assert n_groups == 2
+        assert sorted(grads) == sorted(want)
+        for k, v in grads.items():  # equal shards: the mean of the shard means is the full-batch mean
+            assert nerr(v, want[k]) <= 5e-6, k
