@@ -766,29 +766,49 @@ def model_edges(widths):
 def run_mnist(run: Run):
     """MNIST-shaped classifier: QKAN [784,128,10], reps 3, float32, batch 1024 per GPU, cross-entropy, Adam 1e-3.
     A step is forward, loss, backward, gradient averaging over the ranks and the optimiser update."""
-    torch, args, dev, world, rank = run.torch, run.args, run.dev, run.world, run.rank
+    torch, dist, args, dev, world, rank = run.torch, run.dist, run.args, run.dev, run.world, run.rank
     from qkan_b200 import QKAN
     from qkan_b200.parallel import OverlappedGradSync
 
     widths, reps, rows = [784, 128, 10], 3, 1024
     model = QKAN(widths, reps=reps, device=dev, seed=0)
     opt = torch.optim.Adam(model.parameters(), lr=1e-3)
-    sync = OverlappedGradSync(model)
     gen = torch.Generator().manual_seed(200 + rank)
     hx = torch.rand(rows, 784, generator=gen).pin_memory()          # pixels ~ U[0,1]
     hlab = torch.randint(0, 10, (rows,), generator=gen).pin_memory()  # labels uniform over 0..9
     x, lab = hx.to(dev), hlab.to(dev)
     loss_fn = torch.nn.CrossEntropyLoss()
+    graphed = not args.eager
+    if graphed:
+        # forward + loss + backward replayed as one CUDA graph (the step is bound by launches at this size); the
+        # gradients land in one flat buffer, averaged over the ranks with a single collective
+        from qkan_b200.graph import make_graphed_train_step
 
-    def step(mark, xx=x, ll=lab):
-        sync.zero_grad()
-        loss = loss_fn(model(xx), ll)
-        mark()
-        loss.backward()
-        sync.finish()
-        mark()
-        opt.step()
-        return loss
+        train = make_graphed_train_step(model, x, lab, loss_fn, opt, flat_grads=True)
+        avg = dist.ReduceOp.AVG if world > 1 else None
+
+        def step(mark, xx=x, ll=lab):
+            loss = train(xx, ll)
+            mark()
+            if world > 1:
+                dist.all_reduce(train.flat, op=avg)
+            mark()
+            opt.step()
+            return loss
+        grad_bytes = train.flat.numel() * 4
+    else:
+        sync = OverlappedGradSync(model)
+
+        def step(mark, xx=x, ll=lab):
+            sync.zero_grad()
+            loss = loss_fn(model(xx), ll)
+            mark()
+            loss.backward()
+            sync.finish()
+            mark()
+            opt.step()
+            return loss
+        grad_bytes = sync.nbytes()
 
     total_max_ms, _, segs, clk, wall = run.time_steps(step, args.steps, args.warmup, marks=2)
     ms = total_max_ms / args.steps
@@ -821,10 +841,12 @@ def run_mnist(run: Run):
             "roofline": {"bound": "launch/latency at this size; issue roofline for reference", "roofline_ms": roof_ms,
                          "frac": roof_ms / ms, "peak": PEAK_ISSUE, "unit": "Tlane-op/s",
                          "achieved": roof_ms / ms * PEAK_ISSUE,
-                         "forward_loss_ms": segs[0], "backward_sync_ms": segs[1], "optimizer_ms": segs[2]},
+                         "segments_ms": dict(zip(("graph_forward_loss_backward", "gradient_all_reduce", "optimizer")
+                                                 if graphed else ("forward_loss", "backward_sync", "optimizer"), segs)),
+                         "mode": "CUDA-graph replay of forward + loss + backward" if graphed else "eager"},
             "e2e": {"value": edges * world * reps / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": hx.numel() * 4 + hlab.numel() * 8, "d2h_bytes_per_step": 4},
-            "gpu_launches": 8 * args.steps, "gradient_bytes_per_step": sync.nbytes(), "clocks": clk,
+            "gpu_launches": 8 * args.steps, "gradient_bytes_per_step": grad_bytes, "clocks": clk,
             "wall_s_timed_region": wall,
         }
         print(json.dumps(line))
@@ -964,6 +986,7 @@ def main():
     ap.add_argument("--sweep-widths", type=int, nargs="*", help="bf16_sweep: subset of the layer widths")
     ap.add_argument("--sweep-reps", type=int, nargs="*", help="bf16_sweep: subset of the repetition counts")
     ap.add_argument("--hqkan-layers", type=int, default=12)
+    ap.add_argument("--eager", action="store_true", help="mnist: eager step with per-layer gradient buckets instead of the CUDA-graph step")
     ap.add_argument("--baseline-arm", choices=("flash", "cute"), help=argparse.SUPPRESS)
     args = ap.parse_args()
     if args.baseline_arm:

@@ -51,11 +51,15 @@ def make_graphed_inference(model: nn.Module, sample_input: torch.Tensor,
 def make_graphed_train_step(model: nn.Module, sample_input: torch.Tensor, sample_target: torch.Tensor,
                             loss_fn: Callable[[torch.Tensor, torch.Tensor], torch.Tensor],
                             optimizer: torch.optim.Optimizer,
-                            warmup: int = 3) -> Callable[[torch.Tensor, torch.Tensor], torch.Tensor]:
+                            warmup: int = 3, flat_grads: bool = False) -> Callable[[torch.Tensor, torch.Tensor], torch.Tensor]:
     """Capture forward + loss + gradients; ``optimizer.step()`` stays with the caller.
 
     After ``loss = step(x, y)`` every trainable parameter's ``.grad`` holds this step's gradient
     (static buffers, overwritten by the next call) and ``loss`` is a static scalar tensor.
+
+    ``flat_grads=True`` gathers the gradients, inside the graph, into one flat float32 buffer (``step.flat``) of
+    which the ``.grad`` tensors are views: a data-parallel loop then needs a single all-reduce of ``step.flat``
+    between ``step(x, y)`` and ``optimizer.step()``. Parameters without a gradient get zeros.
     """
     static_x = sample_input.detach().clone()
     static_t = sample_target.detach().clone()
@@ -73,10 +77,27 @@ def make_graphed_train_step(model: nn.Module, sample_input: torch.Tensor, sample
         loss = loss_fn(torch.func.functional_call(model, leaves, (static_x,)), static_t)
         return loss, torch.autograd.grad(loss, list(leaves.values()), allow_unused=True)
 
-    _warm(loss_and_grads, warmup)
-    graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(graph):
-        static_loss, static_grads = loss_and_grads()
+    def loss_and_flat():
+        loss, grads = loss_and_grads()
+        pieces = [(g if g is not None else torch.zeros_like(p)).reshape(-1).to(torch.float32)
+                  for g, p in zip(grads, params)]
+        return loss, torch.cat(pieces)
+
+    flat = None
+    if flat_grads:
+        _warm(loss_and_flat, warmup)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            static_loss, flat = loss_and_flat()
+        static_grads, off = [], 0
+        for p in params:
+            static_grads.append(flat[off: off + p.numel()].view_as(p))
+            off += p.numel()
+    else:
+        _warm(loss_and_grads, warmup)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            static_loss, static_grads = loss_and_grads()
 
     def train_step(x: torch.Tensor, target: torch.Tensor) -> torch.Tensor:
         if x.shape != static_x.shape or target.shape != static_t.shape:
@@ -85,7 +106,8 @@ def make_graphed_train_step(model: nn.Module, sample_input: torch.Tensor, sample
         static_t.copy_(target)
         graph.replay()
         for p, g in zip(params, static_grads):  # re-attach: an optimizer.zero_grad() in between is harmless
-            p.grad = g
+            p.grad = g if g is None or g.dtype == p.dtype else g.to(p.dtype)
         return static_loss
 
+    train_step.flat = flat
     return train_step

@@ -191,6 +191,16 @@ def test_graphed_train_step_and_inference_match_eager():
         for n, p in model.named_parameters():
             if n in eager:
                 assert nerr(p.grad.cpu().numpy(), eager[n].cpu().numpy()) <= 1e-6, n
+    # the same step with the gradients gathered into one flat buffer inside the graph (one all-reduce would do)
+    flat_step = make_graphed_train_step(model, x, labels, loss_fn, opt, flat_grads=True)
+    flat_step(x, labels)
+    torch.cuda.synchronize()
+    n_trainable = sum(p.numel() for p in model.parameters() if p.requires_grad)
+    assert flat_step.flat.numel() == n_trainable
+    for n, p in model.named_parameters():
+        if n in eager:
+            assert p.grad.data_ptr() >= flat_step.flat.data_ptr()  # a view of the flat buffer
+            assert nerr(p.grad.cpu().numpy(), eager[n].cpu().numpy()) <= 1e-6, n
     model.eval()
     with torch.no_grad():
         y_e = model(x)
