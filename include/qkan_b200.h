@@ -223,7 +223,7 @@ int qk_pz_forward_noalloc(const QkDesc* desc, const void* x, const float* theta,
  * Developer overrides of the tile choice, process-wide; no counterpart in the reference (its batch-tile
  * heuristic, src/qkan/_kernel_utils.py:18-31, is fixed). 0 restores the library's own choice. On first use the
  * values are seeded once from the environment variables QK_BWD_GROUPS, QK_BWD_RPG, QK_BWD_RU, QK_BWD_OSPLIT,
- * QK_NO_XTRIG, QK_DEBUG, QK_FWD_THREADS, QK_FWD_TB and QK_FWD_OT; the launch path itself never reads the
+ * QK_NO_XTRIG, QK_DEBUG, QK_FWD_THREADS, QK_FWD_TB, QK_FWD_OT and QK_FWD_ICH; the launch path itself never reads the
  * environment. Workspace sizes depend on the
  * tile choice: query them after setting an override, and do not change one between a size query and its call.
  */
@@ -236,7 +236,8 @@ enum QkDebugKey {
     QK_DBG_VERBOSE = 5,    /* non-zero: print the chosen tiles to stderr */
     QK_DBG_FWD_THREADS = 6, /* threads per forward CTA (multiple of 32, <= 512); needs the next two as well */
     QK_DBG_FWD_TB = 7,      /* batch rows per forward CTA (multiple of 32) */
-    QK_DBG_FWD_OT = 8       /* outputs per forward CTA */
+    QK_DBG_FWD_OT = 8,      /* outputs per forward CTA */
+    QK_DBG_FWD_ICH = 9      /* input columns the forward stages at a time (256, 128 or 64) */
 };
 void qk_debug_set(int key, int value);
 

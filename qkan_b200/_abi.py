@@ -27,7 +27,7 @@ QK_PRECISE_MATH = 8
 QK_SINGLE_TABLE = 16
 
 (QK_DBG_BWD_GROUPS, QK_DBG_BWD_RPG, QK_DBG_BWD_RU, QK_DBG_BWD_OSPLIT, QK_DBG_NO_XTRIG, QK_DBG_VERBOSE,
- QK_DBG_FWD_THREADS, QK_DBG_FWD_TB, QK_DBG_FWD_OT) = range(9)
+ QK_DBG_FWD_THREADS, QK_DBG_FWD_TB, QK_DBG_FWD_OT, QK_DBG_FWD_ICH) = range(10)
 
 QK_OK = 0
 QK_ERR_BAD_ARGUMENT = -1

@@ -13,7 +13,7 @@ constexpr int kGyChunkHost = 8;  // must match kGyChunk of the backward kernel
 
 // Developer overrides of the tile choice (0 = none). They are process-wide values set through qk_debug_set;
 // the first use seeds them, once, from the environment variables of the same names (QK_BWD_GROUPS, QK_BWD_RPG,
-// QK_BWD_RU, QK_BWD_OSPLIT, QK_NO_XTRIG, QK_DEBUG, QK_FWD_THREADS, QK_FWD_TB, QK_FWD_OT), so the launch path
+// QK_BWD_RU, QK_BWD_OSPLIT, QK_NO_XTRIG, QK_DEBUG, QK_FWD_THREADS, QK_FWD_TB, QK_FWD_OT, QK_FWD_ICH), so the launch path
 // itself never reads the environment.
 static std::atomic<int> g_debug[kDbgCount];
 static std::once_flag g_debug_once;
@@ -21,7 +21,7 @@ static std::once_flag g_debug_once;
 static void debug_seed() {
     static const char* const names[kDbgCount] = {"QK_BWD_GROUPS", "QK_BWD_RPG", "QK_BWD_RU",
                                                  "QK_BWD_OSPLIT", "QK_NO_XTRIG", "QK_DEBUG",
-                                                 "QK_FWD_THREADS", "QK_FWD_TB", "QK_FWD_OT"};
+                                                 "QK_FWD_THREADS", "QK_FWD_TB", "QK_FWD_OT", "QK_FWD_ICH"};
     for (int k = 0; k < kDbgCount; ++k) {
         const char* v = getenv(names[k]);
         g_debug[k].store(v && *v ? (atoi(v) != 0 ? atoi(v) : 1) : 0, std::memory_order_relaxed);
@@ -68,7 +68,8 @@ FwdCfg choose_fwd_cfg(const QkDesc& d, bool edges, bool base, bool xtrig) {
     if (f_threads > 0 && f_tb > 0 && f_ot > 0) {  // developer override
         FwdCfg c{};
         c.threads = f_threads;
-        c.ich = ipad < 256 ? ipad : 256;
+        const int ich_o = tune_int(kDbgFwdIch, 256);
+        c.ich = ipad < ich_o ? ipad : ich_o;
         c.tb = round_up(f_tb, 32);
         c.ot = d.out_dim < f_ot ? d.out_dim : f_ot;
         c.grid_b = (d.batch + c.tb - 1) / c.tb;
@@ -76,29 +77,37 @@ FwdCfg choose_fwd_cfg(const QkDesc& d, bool edges, bool base, bool xtrig) {
         c.smem = (size_t)c.tb * c.ich * 4 * ((xtrig ? 2 : 1) + (base ? 1 : 0)) + (edges ? 0 : (size_t)c.ot * (c.tb + 1) * 4);
         if (c.smem <= (size_t)kSmemCap) return c;
     }
+    const int f_ich = tune_int(kDbgFwdIch, 0);
     for (int tb : {64, 32}) {
-        for (int ot = 256; ot >= 1; ot /= 2) {
-            FwdCfg c{};
-            c.threads = 512;
-            c.ich = ipad < 256 ? ipad : 256;
-            c.tb = tb;
-            c.ot = d.out_dim < ot ? d.out_dim : ot;
-            if (c.ot < 16 && c.ot < d.out_dim) continue;  // fewer outputs than warps: idle warps
-            c.grid_b = (d.batch + tb - 1) / tb;
-            c.grid_o = (d.out_dim + c.ot - 1) / c.ot;
-            c.smem = (size_t)tb * c.ich * 4 * ((xtrig ? 2 : 1) + (base ? 1 : 0)) +
-                     (edges ? 0 : (size_t)c.ot * (tb + 1) * 4);
-            if (c.smem > 200 * 1024) continue;
-            const long ctas = (long)c.grid_b * c.grid_o;
-            const long per_sm = (ctas + kSmCount - 1) / kSmCount;  // one CTA of 16 warps per SM at a time
-            // constant loads per (o, 32 columns); warps that own a single output each stay in step
-            // between barriers and expose that load latency together
-            const double per_warp = c.ot / 16.0 < 1.0 ? 1.0 : c.ot / 16.0;
-            const double setup = 1.0 + (0.6 + 8.0 / per_warp) / tb;
-            const double cost = (double)per_sm * tb * c.ot * setup;
-            if (best_cost < 0 || cost < best_cost * 0.999) {
-                best = c;
-                best_cost = cost;
+        // columns staged at a time: 256 unless the tile would not fit (the frozen-preact form stages two floats per
+        // element and the base term a third), then 128 or 64, so that the 64-row tile stays available
+        for (int ich_want : {256, 128, 64}) {
+            if (f_ich > 0 && ich_want != f_ich) continue;
+            if (ich_want < 256 && ipad <= ich_want) continue;  // same tile as the wider candidate
+            for (int ot = 256; ot >= 1; ot /= 2) {
+                FwdCfg c{};
+                c.threads = 512;
+                c.ich = ipad < ich_want ? ipad : ich_want;
+                c.tb = tb;
+                c.ot = d.out_dim < ot ? d.out_dim : ot;
+                if (c.ot < 16 && c.ot < d.out_dim) continue;  // fewer outputs than warps: idle warps
+                c.grid_b = (d.batch + tb - 1) / tb;
+                c.grid_o = (d.out_dim + c.ot - 1) / c.ot;
+                c.smem = (size_t)tb * c.ich * 4 * ((xtrig ? 2 : 1) + (base ? 1 : 0)) +
+                         (edges ? 0 : (size_t)c.ot * (tb + 1) * 4);
+                if (c.smem > 200 * 1024) continue;
+                const long ctas = (long)c.grid_b * c.grid_o;
+                const long per_sm = (ctas + kSmCount - 1) / kSmCount;  // one CTA of 16 warps per SM at a time
+                // constant loads per (o, 32 columns); warps that own a single output each stay in step
+                // between barriers and expose that load latency together
+                const double per_warp = c.ot / 16.0 < 1.0 ? 1.0 : c.ot / 16.0;
+                const double setup = 1.0 + (0.6 + 8.0 / per_warp) / tb;
+                const double restage = 1.0 + 0.01 * (256.0 / ich_want - 1.0);  // more staging rounds and barriers
+                const double cost = (double)per_sm * tb * c.ot * setup * restage;
+                if (best_cost < 0 || cost < best_cost * 0.999) {
+                    best = c;
+                    best_cost = cost;
+                }
             }
         }
     }

@@ -133,7 +133,13 @@ __global__ void QK_FWD_REGCAP forward_kernel(FwdArgs a) {
                             if constexpr (XTRIG) {
                                 const float2 t0 = reinterpret_cast<const float2*>(x_s)[(rg + r) * ich + col];
                                 const float2 t1 = reinterpret_cast<const float2*>(x_s)[(rg + r + 1) * ich + col];
-                                p2 = edge_forward_xtrig2<R, FAST>(e2, make_float2(t0.x, t1.x), make_float2(t0.y, t1.y));
+                                constexpr int kScalarEveryX = QK_FWD_SCALAR_EVERY > 0 ? QK_FWD_SCALAR_EVERY : 1;
+                                if (QK_FWD_SCALAR_EVERY > 0 && ((r / 2) % kScalarEveryX) == kScalarEveryX - 1) {
+                                    p2.x = edge_forward_xtrig<R, FAST>(e, t0.x, t0.y);
+                                    p2.y = edge_forward_xtrig<R, FAST>(e, t1.x, t1.y);
+                                } else {
+                                    p2 = edge_forward_xtrig2<R, FAST>(e2, make_float2(t0.x, t1.x), make_float2(t0.y, t1.y));
+                                }
                             } else {
                                 const f2 x2 = make_float2(x_s[(rg + r) * ich + col], x_s[(rg + r + 1) * ich + col]);
                                 constexpr int kScalarEvery = QK_FWD_SCALAR_EVERY > 0 ? QK_FWD_SCALAR_EVERY : 1;

@@ -106,7 +106,7 @@ struct BaseBwdArgs {
 FwdCfg choose_fwd_cfg(const QkDesc& d, bool edges, bool base, bool xtrig);
 
 // Developer overrides (qk_debug_set in the C ABI; first use also reads the QK_* environment variables once).
-enum DebugKey { kDbgBwdGroups = 0, kDbgBwdRpg, kDbgBwdRu, kDbgBwdOsplit, kDbgNoXtrig, kDbgVerbose, kDbgFwdThreads, kDbgFwdTb, kDbgFwdOt, kDbgCount };
+enum DebugKey { kDbgBwdGroups = 0, kDbgBwdRpg, kDbgBwdRu, kDbgBwdOsplit, kDbgNoXtrig, kDbgVerbose, kDbgFwdThreads, kDbgFwdTb, kDbgFwdOt, kDbgFwdIch, kDbgCount };
 int debug_get(int key);
 void debug_set(int key, int value);
 
