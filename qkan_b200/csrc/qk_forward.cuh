@@ -50,7 +50,15 @@ __device__ __forceinline__ float silu_f(float v) { return v / (1.f + expf(-v)); 
 #define QK_FWD_POLY_EVERY 1
 #endif
 #ifndef QK_XTRIG_PACKED
-#define QK_XTRIG_PACKED 0
+#define QK_XTRIG_PACKED 1
+#endif
+// 1: a lane adds up its columns of the staged chunk (all 32-column blocks) in its 32 row registers before the
+// shuffle reduction over the lanes, so that reduction (about 4 instructions per edge and row) is paid once per
+// chunk instead of once per 32-column block; the constants of a column block are then fetched once per 32 rows.
+// 0: one shuffle reduction per 32-column block. Measured at 65536 x 256 -> 256, 3 repetitions (forward, ms): 8.06 -> 7.76
+// trainable preacts, 8.43 -> 8.01 with the base term, 7.33 -> 7.22 (scalar) / 6.75 (packed) frozen preacts.
+#ifndef QK_FWD_SUM_COLUMNS
+#define QK_FWD_SUM_COLUMNS 1
 #endif
 // One row pair in QK_FWD_SCALAR_EVERY is evaluated as two scalar rows; 0 = every pair packed. Measured at the
 // headline shape (forward, ms): 0: 8.05; every 4th 8.09, every 3rd 8.17, every 2nd 8.30: mixing does not pay.
@@ -109,21 +117,27 @@ __global__ void QK_FWD_REGCAP forward_kernel(FwdArgs a) {
         const int nsub = w / kWarp;
         for (int ol = warp; ol < ot_eff; ol += nwarps) {
             const int o = o0 + ol;
+            constexpr bool kSumCols = QK_FWD_SUM_COLUMNS != 0 && !EDGES;
+            for (int rg_outer = 0; rg_outer < (kSumCols ? tb : 1); rg_outer += 32) {
+            float v[32];
+            if constexpr (kSumCols) {
+#pragma unroll
+                for (int r = 0; r < 32; ++r) v[r] = 0.f;
+            }
             for (int sub = 0; sub < nsub; ++sub) {
                 const int col = sub * kWarp + lane;
                 const int i = ic0 + col;
                 EdgeFwd<R> e;
                 e.load(a.table + ((size_t)o * a.ipad + i) * KS);
                 const float bw = e.bw;
-                // (the frozen-preact form gains nothing from packing, 7.31 against 7.32 ms: it is all FMA-pipe work, which the
-                // packed operations do not speed up; QK_XTRIG_PACKED = 1 selects it anyway)
+                // (the frozen-preact form: packed 6.75 against 7.22 ms scalar once the columns are summed before the
+                // shuffle reduction; with one reduction per column block the two were equal, 7.31 / 7.32 ms)
                 constexpr bool kPacked = QK_PACKED_F32 != 0 && !PRECISE && (!XTRIG || QK_XTRIG_PACKED != 0) && R >= 1 && R <= 12;
                 constexpr int kPolyGates = R < QK_FWD_POLY_GATES ? R : QK_FWD_POLY_GATES;
                 constexpr int kEvery = QK_FWD_POLY_EVERY > 0 ? QK_FWD_POLY_EVERY : 1;
                 EdgePk<R> e2;
                 if constexpr (kPacked) e2.from(e);
-                for (int rg = 0; rg < tb; rg += 32) {
-                    float v[32];
+                for (int rg = kSumCols ? rg_outer : 0; rg < (kSumCols ? rg_outer + 32 : tb); rg += 32) {
                     if constexpr (kPacked) {
                         // two rows per instruction (qk_packed.cuh); pair q = r / 2 takes its first kPolyGates data
                         // gates from the polynomial when q % kEvery == kEvery - 1
@@ -159,7 +173,7 @@ __global__ void QK_FWD_REGCAP forward_kernel(FwdArgs a) {
                                 v[r] = p2.x;
                                 v[r + 1] = p2.y;
                             } else {
-                                f2 val = mul2(p2, e2.w);
+                                f2 val = kSumCols ? fma2(p2, e2.w, make_float2(v[r], v[r + 1])) : mul2(p2, e2.w);
                                 if (BASE)
                                     val = fma2(make_float2(b_s[(rg + r) * ich + col], b_s[(rg + r + 1) * ich + col]), pk(bw), val);
                                 v[r] = val.x;
@@ -185,7 +199,7 @@ __global__ void QK_FWD_REGCAP forward_kernel(FwdArgs a) {
                         if (EDGES) {
                             v[r] = p;
                         } else {
-                            float val = p * e.w;
+                            float val = kSumCols ? fmaf(p, e.w, v[r]) : p * e.w;
                             if (BASE) val = fmaf(b_s[(rg + r) * ich + col], bw, val);
                             v[r] = val;
                         }
@@ -200,11 +214,16 @@ __global__ void QK_FWD_REGCAP forward_kernel(FwdArgs a) {
                                     st_from_float(out + ((size_t)(b0 + rg + r) * a.out_dim + o) * a.in_dim + i,
                                                   v[r]);
                         }
-                    } else {
+                    } else if (!kSumCols) {
                         float s = transpose_reduce32(v, lane);
                         y_s[ol * ldy + rg + lane] += s;
                     }
                 }
+            }
+            if constexpr (kSumCols) {
+                float s = transpose_reduce32(v, lane);
+                y_s[ol * ldy + rg_outer + lane] += s;
+            }
             }
         }
     }
