@@ -34,6 +34,59 @@ __device__ __forceinline__ float transpose_reduce32(float (&v)[32], int lane) {
 
 __device__ __forceinline__ float silu_f(float v) { return v / (1.f + expf(-v)); }
 
+// Staging of one x tile (tb rows x w columns from column ic0) into shared memory: a warp takes whole rows; its lanes
+// read 16 bytes each (4 float32 / 8 bfloat16 values), so a row segment is fetched with coalesced 128-bit loads. Rows
+// whose segments are not 16-byte aligned (in_dim not a multiple of the vector, or an unaligned x) and the ragged right
+// edge take the element-wise path. XTRIG stores (cos x, sin x), BASE also silu(x). Out of line on purpose: the
+// register allocation of the kernel's main loop then does not depend on this code.
+template <typename IO, bool BASE, bool XTRIG>
+static __device__ __noinline__ void stage_x_tile(const IO* __restrict__ x, int batch, int in_dim, int b0, int ic0, int w,
+                                                 int tb, int ich, float* __restrict__ x_s, float* __restrict__ b_s) {
+    const int warp = threadIdx.x / kWarp, lane = threadIdx.x % kWarp;
+    const int nwarps = blockDim.x / kWarp;
+    constexpr int VEC = 16 / (int)sizeof(IO);
+    const bool vec_ok = (in_dim % VEC) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0;
+    auto put = [&](int r, int c, float v) {
+        if (XTRIG) {
+            float sx, cx;
+            precise_sincos(v, sx, cx);
+            reinterpret_cast<float2*>(x_s)[r * ich + c] = make_float2(cx, sx);
+        } else {
+            x_s[r * ich + c] = v;
+        }
+        if (BASE) b_s[r * ich + c] = silu_f(v);
+    };
+    for (int r = warp; r < tb; r += nwarps) {
+        const bool row_ok = b0 + r < batch;
+        const IO* xr = x + (size_t)(b0 + r) * in_dim + ic0;
+        for (int c = lane * VEC; c < w; c += kWarp * VEC) {
+            if (vec_ok && row_ok && ic0 + c + VEC <= in_dim) {
+                const uint4 q = __ldg(reinterpret_cast<const uint4*>(xr + c));
+                if constexpr (sizeof(IO) == 4) {
+                    put(r, c, __uint_as_float(q.x));
+                    put(r, c + 1, __uint_as_float(q.y));
+                    put(r, c + 2, __uint_as_float(q.z));
+                    put(r, c + 3, __uint_as_float(q.w));
+                } else {
+                    const unsigned wd[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {  // bfloat16 is the upper half of a float32
+                        put(r, c + 2 * k, __uint_as_float(wd[k] << 16));
+                        put(r, c + 2 * k + 1, __uint_as_float(wd[k] & 0xffff0000u));
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int k = 0; k < VEC; ++k) {
+                    float v = 0.f;
+                    if (row_ok && ic0 + c + k < in_dim) v = ld_as_float(xr + c + k);
+                    put(r, c + k, v);
+                }
+            }
+        }
+    }
+}
+
 // One row pair in QK_FWD_POLY_EVERY of a lane's 32-row block (one row, in the scalar form) evaluates the sin/cos of
 // its first QK_FWD_POLY_GATES data gates on the FMA pipe (poly_sincos) instead of the special-function unit, which
 // bounds this kernel; 0 switches that off. Packed form (two rows per instruction), forward ms at 65536 x 256 -> 256,
@@ -99,20 +152,7 @@ __global__ void QK_FWD_REGCAP forward_kernel(FwdArgs a) {
     for (int ic0 = 0; ic0 < a.ipad; ic0 += ich) {
         const int w = min(ich, a.ipad - ic0);  // multiple of 32
         __syncthreads();
-        for (int idx = threadIdx.x; idx < tb * w; idx += blockDim.x) {
-            int r = idx / w, c = idx - r * w;
-            float v = 0.f;
-            if (b0 + r < a.batch && ic0 + c < a.in_dim)
-                v = ld_as_float(x + (size_t)(b0 + r) * a.in_dim + ic0 + c);
-            if (XTRIG) {
-                float sx, cx;
-                precise_sincos(v, sx, cx);
-                reinterpret_cast<float2*>(x_s)[r * ich + c] = make_float2(cx, sx);
-            } else {
-                x_s[r * ich + c] = v;
-            }
-            if (BASE) b_s[r * ich + c] = silu_f(v);
-        }
+        stage_x_tile<IO, BASE, XTRIG>(x, a.batch, a.in_dim, b0, ic0, w, tb, ich, x_s, b_s);
         __syncthreads();
         const int nsub = w / kWarp;
         for (int ol = warp; ol < ot_eff; ol += nwarps) {
