@@ -73,7 +73,7 @@ def install(src: str, with_cuda: bool = True) -> int:
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--src", default="/root/reference")
+    ap.add_argument("--src", default=os.environ.get("QKAN_REFERENCE_ROOT", "/root/reference"))
     ap.add_argument("--no-cuda", action="store_true", help="pure-Python install (exact and flash arms only)")
     a = ap.parse_args()
     sys.exit(install(a.src, with_cuda=not a.no_cuda))
