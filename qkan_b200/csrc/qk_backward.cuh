@@ -111,6 +111,45 @@ constexpr int kGyChunk = 8;  // outputs whose grad_y columns are staged together
 #define QK_BWD_HYBRID 0
 #endif
 
+// grad_y[b0 .. b0+tb, oc .. oc+nch) into shared memory, transposed ([output][row]); rows past the batch read as 0.
+// QK_BWD_STAGE_NOINLINE = 1 keeps it out of line (the main loop's register allocation then does not depend on it).
+#ifndef QK_BWD_STAGE_NOINLINE
+#define QK_BWD_STAGE_NOINLINE 1
+#endif
+#if QK_BWD_STAGE_NOINLINE
+#define QK_STAGE_LINKAGE static __device__ __noinline__
+#else
+#define QK_STAGE_LINKAGE static __device__ __forceinline__
+#endif
+template <typename IO>
+QK_STAGE_LINKAGE void stage_grad_y(const IO* __restrict__ gsrc, int batch, int out_dim, int b0, int oc, int nch, int tb,
+                                   float* __restrict__ gy_s) {
+    if (std::is_same<IO, float>::value && nch == kGyChunk && (out_dim & 3) == 0 &&
+        (reinterpret_cast<uintptr_t>(gsrc) & 15) == 0) {
+        // full chunk of float32 rows from a 16-byte aligned grad_y: two 128-bit loads per row
+        // (oc and out_dim are multiples of 4, so every row segment is aligned too)
+        for (int idx = threadIdx.x; idx < tb * 2; idx += blockDim.x) {
+            const int r = idx >> 1, h = idx & 1;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (b0 + r < batch)
+                v = __ldg(reinterpret_cast<const float4*>(
+                    reinterpret_cast<const float*>(gsrc) + (size_t)(b0 + r) * out_dim + oc + 4 * h));
+            float* dst = gy_s + (4 * h) * tb + r;
+            dst[0] = v.x;
+            dst[tb] = v.y;
+            dst[2 * tb] = v.z;
+            dst[3 * tb] = v.w;
+        }
+    } else {
+        for (int idx = threadIdx.x; idx < tb * kGyChunk; idx += blockDim.x) {
+            const int r = idx / kGyChunk, c = idx % kGyChunk;
+            float v = 0.f;
+            if (b0 + r < batch && c < nch) v = ld_as_float(gsrc + (size_t)(b0 + r) * out_dim + oc + c);
+            gy_s[c * tb + r] = v;
+        }
+    }
+}
+
 // Register cap of the short circuits (up to 3 repetitions): two CTAs of 256 threads stay resident per SM and the
 // compiler spends the rest on scheduling; 4 to 8 repetitions are capped at 128 (still two CTAs: uncapped, the
 // 8-repetition kernel took 152 registers, lost its second CTA and a fifth of its speed); the padded 12- and
@@ -123,16 +162,17 @@ constexpr int kGyChunk = 8;  // outputs whose grad_y columns are staged together
 #ifndef QK_BWD_SHORT_MAXNREG
 #define QK_BWD_SHORT_MAXNREG 112
 #endif
-#ifdef QK_BWD_COLSUM_NOINLINE
-#define QK_COLSUM_LINKAGE static __device__ __noinline__
-#else
+#ifdef QK_BWD_COLSUM_INLINE
 #define QK_COLSUM_LINKAGE static __device__ __forceinline__
+#else
+#define QK_COLSUM_LINKAGE static __device__ __noinline__
 #endif
 
 // Column sums of one batch tile's staged grad_y rows (the postact-bias terms need sum_b grad_y[b,o]): taken by
 // the CTAs of column block 0 only, one warp per output, lane-strided partial sums and a shuffle tree (fixed
-// order); finish_grads adds the tiles in order. (Inlined: measured 3 % faster at the headline shape than the
-// out-of-line call, through nothing but a different instruction schedule of the hot loop.)
+// order); finish_grads adds the tiles in order. Out of line, like the staging of grad_y: with the packed main loop
+// that measured 1 % faster than inlining both (14.18 against 14.31 ms at the headline shape; in the scalar build it
+// was the other way round by 3 %, through nothing but a different instruction schedule of the hot loop).
 QK_COLSUM_LINKAGE void tile_column_sums(float* __restrict__ dst, const float* gy_s, int nch, int groups, int tb) {
     const int lane = threadIdx.x % kWarp, grp = threadIdx.x / kWarp;
     for (int c = grp; c < nch; c += groups) {
@@ -181,32 +221,7 @@ __global__ void __launch_bounds__(256) __maxnreg__(R <= 3 ? QK_BWD_SHORT_MAXNREG
     for (int oc = o_begin; oc < o_end; oc += kGyChunk) {
         const int nch = min(kGyChunk, o_end - oc);
         if (!EDGES) {
-            // stage grad_y[b0 .. b0+tb, oc .. oc+nch) transposed; rows past the batch read as 0
-            if (std::is_same<IO, float>::value && nch == kGyChunk && (a.out_dim & 3) == 0 &&
-                (reinterpret_cast<uintptr_t>(gsrc) & 15) == 0) {
-                // full chunk of float32 rows from a 16-byte aligned grad_y: two 128-bit loads per row
-                // (oc and out_dim are multiples of 4, so every row segment is aligned too)
-                for (int idx = threadIdx.x; idx < tb * 2; idx += blockDim.x) {
-                    const int r = idx >> 1, h = idx & 1;
-                    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (b0 + r < a.batch)
-                        v = __ldg(reinterpret_cast<const float4*>(
-                            reinterpret_cast<const float*>(gsrc) + (size_t)(b0 + r) * a.out_dim + oc + 4 * h));
-                    float* dst = gy_s + (4 * h) * tb + r;
-                    dst[0] = v.x;
-                    dst[tb] = v.y;
-                    dst[2 * tb] = v.z;
-                    dst[3 * tb] = v.w;
-                }
-            } else {
-                for (int idx = threadIdx.x; idx < tb * kGyChunk; idx += blockDim.x) {
-                    const int r = idx / kGyChunk, c = idx % kGyChunk;
-                    float v = 0.f;
-                    if (b0 + r < a.batch && c < nch)
-                        v = ld_as_float(gsrc + (size_t)(b0 + r) * a.out_dim + oc + c);
-                    gy_s[c * tb + r] = v;
-                }
-            }
+            stage_grad_y<IO>(gsrc, a.batch, a.out_dim, b0, oc, nch, tb, gy_s);
             __syncthreads();
             if (a.colpart && blockIdx.y == 0)
                 tile_column_sums(a.colpart + (size_t)bt * a.out_dim + oc, gy_s, nch, groups, tb);
