@@ -20,8 +20,17 @@ constexpr int kBaseChunk = 8;  // outputs per staged grad_y chunk; equal to the 
 
 __device__ __forceinline__ float sigmoid_f(float v) { return 1.f / (1.f + expf(-v)); }
 
+#ifndef QK_BASE_MINB
+#define QK_BASE_MINB 3
+#endif
+#ifndef QK_BASE_UNROLL
+#define QK_BASE_UNROLL 2
+#endif
+#define QK_PRAGMA(x) _Pragma(#x)
+#define QK_UNROLL(n) QK_PRAGMA(unroll n)
+
 template <typename IO, int RPW>
-__global__ void __launch_bounds__(kBaseWarps * kWarp, 3) base_backward_kernel(BaseBwdArgs a) {
+__global__ void __launch_bounds__(kBaseWarps * kWarp, QK_BASE_MINB) base_backward_kernel(BaseBwdArgs a) {
     constexpr int TB = kBaseWarps * RPW;  // rows per CTA
     constexpr int LD = TB + 4;            // staged row length: keeps 128-bit alignment, spreads the banks
     __shared__ __align__(16) float gy_s[2][kBaseChunk][LD];
@@ -34,13 +43,20 @@ __global__ void __launch_bounds__(kBaseWarps * kWarp, 3) base_backward_kernel(Ba
     const IO* __restrict__ x = static_cast<const IO*>(a.x);
     const IO* __restrict__ gy = static_cast<const IO*>(a.gy);
 
-    float sl[RPW], gxb[RPW];
+    // silu(x) and the running grad_x sums of the thread's rows, held as row pairs (two rows per instruction on
+    // the packed float32 operations; the staged grad_y vector delivers the matching pairs)
+    f2 sl2[RPW / 2], gxb2[RPW / 2];
 #pragma unroll
-    for (int r = 0; r < RPW; ++r) {
-        const int b = b0 + row0 + r;
-        const float v = (b < a.batch && col_ok) ? ld_as_float(x + (size_t)b * a.in_dim + i) : 0.f;
-        sl[r] = v * sigmoid_f(v);
-        gxb[r] = 0.f;
+    for (int r = 0; r < RPW; r += 2) {
+        float v[2];
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            const int b = b0 + row0 + r + k;
+            const float xv = (b < a.batch && col_ok) ? ld_as_float(x + (size_t)b * a.in_dim + i) : 0.f;
+            v[k] = xv * sigmoid_f(xv);
+        }
+        sl2[r / 2] = make_float2(v[0], v[1]);
+        gxb2[r / 2] = pk(0.f);
     }
 
     // Software pipeline over chunks of 8 outputs: the next chunk's grad_y tile and base weights are fetched
@@ -70,25 +86,19 @@ __global__ void __launch_bounds__(kBaseWarps * kWarp, 3) base_backward_kernel(Ba
         bw_s[buf][w][lane] = bw_next;
         __syncthreads();
         if (oc + kBaseChunk < a.out_dim) fetch(oc + kBaseChunk);
-#pragma unroll 2
+QK_UNROLL(QK_BASE_UNROLL)
         for (int c = 0; c < kBaseChunk; ++c) {
             const float bw = bw_s[buf][c][lane];
-            // two rows per instruction on the packed float32 operations: the staged grad_y vector and the thread's
-            // silu(x) / grad_x registers are natural row pairs; two independent chains for the batch sum
             const f2 bw2 = pk(bw);
-            f2 sa = pk(0.f), sb = pk(0.f);
+            f2 sa = pk(0.f), sb = pk(0.f);  // two independent chains for the batch sum
 #pragma unroll
             for (int r = 0; r < RPW; r += 4) {
                 const float4 g = *reinterpret_cast<const float4*>(&gy_s[buf][c][row0 + r]);
                 const f2 g01 = make_float2(g.x, g.y), g23 = make_float2(g.z, g.w);
-                const f2 a01 = fma2(g01, bw2, make_float2(gxb[r], gxb[r + 1]));
-                const f2 a23 = fma2(g23, bw2, make_float2(gxb[r + 2], gxb[r + 3]));
-                gxb[r] = a01.x;
-                gxb[r + 1] = a01.y;
-                gxb[r + 2] = a23.x;
-                gxb[r + 3] = a23.y;
-                sa = fma2(g01, make_float2(sl[r], sl[r + 1]), sa);
-                sb = fma2(g23, make_float2(sl[r + 2], sl[r + 3]), sb);
+                gxb2[r / 2] = fma2(g01, bw2, gxb2[r / 2]);
+                gxb2[r / 2 + 1] = fma2(g23, bw2, gxb2[r / 2 + 1]);
+                sa = fma2(g01, sl2[r / 2], sa);
+                sb = fma2(g23, sl2[r / 2 + 1], sb);
             }
             const float s0 = sa.x, s1 = sa.y, s2 = sb.x, s3 = sb.y;
             // written after this chunk's staging barrier, i.e. after the last chunk's reads
@@ -117,7 +127,8 @@ __global__ void __launch_bounds__(kBaseWarps * kWarp, 3) base_backward_kernel(Ba
                 // grad_x is read and written by this kernel: a plain load (the read-only path is for data the
                 // kernel never writes). With bfloat16 activations the circuit share was rounded once when the
                 // backward stored it and the sum is rounded again here (half an ulp each, inside the bf16 bound).
-                st_from_float(gx + at, fmaf(dsl, gxb[r], ld_rw_as_float(gx + at)));
+                const float acc = (r & 1) ? gxb2[r / 2].y : gxb2[r / 2].x;
+                st_from_float(gx + at, fmaf(dsl, acc, ld_rw_as_float(gx + at)));
             }
         }
     }
