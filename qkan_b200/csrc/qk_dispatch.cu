@@ -168,7 +168,7 @@ BwdCfg choose_bwd_cfg(const QkDesc& d) {
                 const double occupancy =
                     warps >= 16 ? 1.0 : (warps >= 8 ? 1.0 + 0.04 * (16 - warps) : 1.32 + 0.2 * (8 - warps));
                 const double setup = 1.0 + 0.09 * 32.0 / cur.rpg;       // per-edge set-up and reduction per row
-                const double small_cta = 1.0 + 0.02 * (8.0 / cur.groups - 1.0);
+                const double small_cta = 1.0 + 0.02 * (8.0 / cur.groups - 1.0);  // (0.06 fits 16384 x 256 x 256 better but costs 512 x 512 at 1 repetition 15 %)
                 const int o_cta = cur.osplit > 1 ? cur.ochunk : d.out_dim;
                 // a partly filled last wave costs less than a full one (its CTAs have the SM's issue slots to
                 // themselves): count it half-way between its share and a whole wave
