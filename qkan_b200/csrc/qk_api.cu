@@ -60,7 +60,7 @@ bool use_xtrig(const QkDesc& d) {
 struct Tables {
     int ipad;
     bool xtrig;
-    size_t table_off, bias_off, tablex_off, total;
+    size_t table_off, bias_off, tablex_off, basew_off, total;
 };
 
 // Scratch of one backward call: per-tile column sums of grad_y, per-tile gradient partials, the base-term
@@ -89,6 +89,9 @@ Tables tables_layout(const QkDesc& d) {
         l.tablex_off = l.total;
         l.total += table;
     }
+    // base_weight * mask once more as a dense [out_dim][ipad] matrix (operand of the base-term backward)
+    l.basew_off = l.total;
+    l.total += qk::align256((size_t)d.out_dim * l.ipad * sizeof(float));
     return l;
 }
 
@@ -99,8 +102,7 @@ Scratch scratch_layout(const QkDesc& d) {
     l.colpart_off = 0;
     l.partials_off = qk::align256((size_t)l.cfg.grid_b * d.out_dim * sizeof(float));
     l.total = l.partials_off + qk::align256((size_t)l.cfg.grid_b * d.out_dim * l.cfg.nacc * ipad * sizeof(float));
-    const int base_tb = qk::base_rows_per_cta(d.batch, d.in_dim);
-    l.base_tiles = (d.batch + base_tb - 1) / base_tb;
+    l.base_tiles = qk::base_plan(d.batch, d.in_dim, d.out_dim).slabs;
     l.basepart_off = l.total;
     l.total += qk::align256((size_t)l.base_tiles * d.out_dim * ipad * sizeof(float));
     if (l.cfg.osplit > 1) {
@@ -166,6 +168,7 @@ int run_prepare(const QkDesc* desc, const float* theta, const float* pw, const f
     p.table = reinterpret_cast<float*>(tb + l.table_off);
     p.table_x = l.xtrig ? reinterpret_cast<float*>(tb + l.tablex_off) : nullptr;
     p.bias = edges ? nullptr : reinterpret_cast<float*>(tb + l.bias_off);
+    p.basew_c = p.basew ? reinterpret_cast<float*>(tb + l.basew_off) : nullptr;
     cudaError_t e = qk::launch_prep(p, st);
     if (e != cudaSuccess) return cuda_fail(e, "prep launch");
     return QK_OK;
@@ -292,11 +295,9 @@ int run_backward_prepared(const QkDesc* desc, const void* x, const void* tables,
         ba.in_dim = d.in_dim;
         ba.out_dim = d.out_dim;
         ba.ipad = tl.ipad;
-        ba.ks = qk::table_stride(rk);
-        ba.bw_row = qk::t_bw(rk);
         ba.x = x;
         ba.gy = gy;
-        ba.table = table;
+        ba.basew = reinterpret_cast<const float*>(static_cast<const char*>(tables) + tl.basew_off);
         ba.gx = gx;
         ba.partials = gbasew ? base_partials : nullptr;
         e = qk::launch_base_backward(ba, d.io_dtype, st);

@@ -22,6 +22,7 @@ struct PrepArgs {
     float* table;    // generic table (backward, and every forward but the frozen-preact one)
     float* table_x;  // frozen-preact forward's table: rows (pw_l, c_l) hold (cos c_l, sin c_l); nullptr => not wanted
     float* bias;     // nullptr => not computed
+    float* basew_c;  // [out_dim][ipad] base_weight * mask for the base-term backward; nullptr => not wanted
 };
 
 struct FinishArgs {
@@ -95,13 +96,22 @@ struct BwdArgs {
 // Backward of the base term (qk_base.cu): runs after the circuit backward, adds its part to grad_x in place.
 struct BaseBwdArgs {
     int batch, in_dim, out_dim, ipad;
-    int ks, bw_row;      // stride of an edge's constants in the table and the row of base_weight * mask within it
+    int slab_rows, slabs;  // filled by the launcher from base_plan()
+    int vec4;              // filled by the launcher: x / grad_x may be moved four columns at a time
+    int vec_gy;            // filled by the launcher: so may grad_y
     const void* x;
     const void* gy;
-    const float* table;
+    const float* basew;  // [out_dim][ipad] base_weight * mask, written by prep
     void* gx;            // read-modify-write; nullptr: grad_x not wanted
-    float* partials;     // [row tiles][out_dim][ipad]; nullptr: grad_base_weight not wanted
+    float* partials;     // [slabs][out_dim][ipad]; nullptr: grad_base_weight not wanted
 };
+
+// Tiling of the base-term backward: tile edge (128 or 64) and the slabs of batch rows whose partial sums of
+// grad_base_weight go to scratch.
+struct BasePlan {
+    int tile, slab_rows, slabs;
+};
+BasePlan base_plan(int batch, int in_dim, int out_dim);
 
 FwdCfg choose_fwd_cfg(const QkDesc& d, bool edges, bool base, bool xtrig);
 
@@ -128,7 +138,6 @@ inline cudaError_t opt_in_smem(K kern, unsigned long long* mask) {
     return e;
 }
 BwdCfg choose_bwd_cfg(const QkDesc& d);
-int base_rows_per_cta(int batch, int in_dim);
 cudaError_t launch_base_backward(const BaseBwdArgs& a, int io_dtype, cudaStream_t st);
 
 cudaError_t launch_prep(const PrepArgs& a, cudaStream_t st);

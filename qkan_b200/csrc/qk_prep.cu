@@ -21,6 +21,7 @@ __device__ void prep_edge(const PrepArgs& a, int o, int i) {
     };
     if (i >= a.in_dim) {
         for (int k = 0; k < K; ++k) put(k, 0.f);
+        if (a.basew_c) a.basew_c[(size_t)o * a.ipad + i] = 0.f;
         return;
     }
     const size_t e = (size_t)o * a.in_dim + i;
@@ -28,6 +29,7 @@ __device__ void prep_edge(const PrepArgs& a, int o, int i) {
     const float m = a.mask ? ld_param(a.mask, a.param_dtype, e) : 1.f;
     const float w = a.postw ? ld_param(a.postw, a.param_dtype, e) * m : 1.f;
     const float bw = a.basew ? ld_param(a.basew, a.param_dtype, e) * m : 0.f;
+    if (a.basew_c) a.basew_c[(size_t)o * a.ipad + i] = bw;  // the base-term backward reads it as a dense matrix
     // rpz always encodes pw*x + pb (src/qkan/solver/exact.py:75-76)
     const bool ptr = (a.flags & QK_PREACT_TRAINABLE) != 0 || a.ansatz == QK_ANSATZ_RPZ;
 

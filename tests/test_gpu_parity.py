@@ -310,6 +310,32 @@ def test_seeded_random_shapes_and_flags_vs_oracle():
             assert nerr(g[k], g_ref[k]) <= TOL_F32, f"{label}: grad {k} err {nerr(g[k], g_ref[k]):.3e}"
 
 
+@pytest.mark.parametrize("B,I,O,io_dtype", [(19205, 202, 70, torch.float32), (19200, 200, 130, torch.float32),
+                                            (19200, 200, 130, torch.bfloat16), (300, 37, 9, torch.float32)],
+                         ids=["ragged-scalar-columns", "two-output-tiles", "bf16", "small-tiles"])
+def test_base_term_backward_products(B, I, O, io_dtype):
+    """The base term's two matrix products (grad_x share and grad_base_weight) at shapes that use the 128-wide
+    tiles, several slabs of batch rows, ragged tile edges and both the four-column and the single-column
+    epilogue, against the oracle; asking for one of the two results alone runs one kind of CTA only and gives
+    the same bits."""
+    from qkan_b200 import functional as F
+
+    R = 1
+    p = random_problem(B + I + O, B, I, O, R, use_pb=True, base=True, masked=True)
+    cfg = dict(preact_trainable=True, fast_measure=True, use_postact_bias=True)
+    bf16 = io_dtype == torch.bfloat16
+    if bf16:
+        for k in ("x", "gy"):  # the oracle sees the bf16-rounded activations
+            p[k] = torch.as_tensor(p[k]).to(torch.bfloat16).float().numpy()
+    y, g = _run_cuda(p, cfg, io_dtype=io_dtype)
+    y_ref, g_ref = _run_oracle(p, cfg)
+    _check(y, g, y_ref, g_ref, TOL_BF16 if bf16 else TOL_F32, f"base term B{B} I{I} O{O}")
+    args = [_dev(p["x"], io_dtype)] + [_dev(p[k]) for k in ("theta", "pw", "pb", "postw", "postb", "basew", "mask")]
+    for name in ("x", "base_weight"):
+        one = F.layer_backward(*args, _dev(p["gy"], io_dtype), want=(name,), **cfg)[name]
+        assert np.array_equal(one.float().cpu().numpy(), g[name]), name
+
+
 def test_grouped_parameters_with_empty_batch_and_bf16():
     """Grouped theta / preacts: an empty batch gives zero gradients in the grouped shapes, and bfloat16
     activations with bfloat16 (O,I) tensors stay inside the bf16 bound against the oracle."""
