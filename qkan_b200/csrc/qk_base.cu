@@ -102,8 +102,9 @@ __device__ __forceinline__ void tile_product(int nk, FA fetch_a, FB fetch_b, SA 
             ra = fetch_a(kt + 1);
             rb = fetch_b(kt + 1);
         }
-        // not unrolled: one step's F/2 loads and F*F/2 packed FMAs already fill the register budget of two CTAs per SM
-#pragma unroll 1
+        // 128-wide tiles: not unrolled (one step's F/2 loads and F*F/2 packed FMAs already fill the register budget of
+        // two CTAs per SM); 64-wide tiles (small, latency-bound problems): unrolled, the shared loads run ahead
+#pragma unroll(F == 8 ? 1 : C::TK)
         for (int k = 0; k < C::TK; ++k) {
             f2 a2[F], b2[F / 2];
 #pragma unroll
@@ -128,7 +129,7 @@ __device__ __forceinline__ void tile_product(int nk, FA fetch_a, FB fetch_b, SA 
 }
 
 template <typename IO, int T>
-__global__ void __launch_bounds__(kBaseThreads, T == 128 ? 2 : 3) base_backward_kernel(BaseBwdArgs a) {
+__global__ void __launch_bounds__(kBaseThreads, 2) base_backward_kernel(BaseBwdArgs a) {
     using C = BaseTile<T>;
     constexpr int F = C::F, TK = C::TK, LDA = C::LDA, LDB = C::LDB;
     __shared__ __align__(16) float As[2][TK * LDA];
@@ -244,15 +245,17 @@ BasePlan base_plan(int batch, int in_dim, int out_dim) {
     const int wave = 148 * (p.tile == 128 ? 2 : 3);
     const long weight_tiles = (long)((out_dim + p.tile - 1) / p.tile) * ((ipad + p.tile - 1) / p.tile);
     // Slabs of batch rows for grad_base_weight: about one wave of CTAs (they are the long ones and are launched
-    // first, the grad_x tiles fill in behind them), no shorter than 16 rows (small problems: many short slabs, i.e.
-    // more CTAs in flight and a flatter summation tree), and no longer than 4096 rows so that a float32 running sum
-    // stays well inside the parity bound.
+    // first, the grad_x tiles fill in behind them), no shorter than 16 rows (small problems are latency-bound: many
+    // short slabs mean short chains of dependent tiles and a flat summation tree), and no longer than 4096 rows so
+    // that a float32 running sum stays well inside the parity bound.
     long slabs = weight_tiles > 0 ? wave / weight_tiles : 1;
     const long most = (batch + 15) / 16, least = (batch + 4095) / 4096;
     if (slabs > most) slabs = most;
     if (slabs < least) slabs = least;
     if (slabs < 1) slabs = 1;
-    p.slab_rows = round_up((int)((batch + slabs - 1) / slabs), 16);
+    const int rows = (int)((batch + slabs - 1) / slabs);
+    p.slab_rows = 16;  // a power of two: whole staged tiles
+    while (p.slab_rows < rows) p.slab_rows *= 2;
     p.slabs = (batch + p.slab_rows - 1) / p.slab_rows;
     if (p.slabs < 1) p.slabs = 1;
     return p;
