@@ -48,7 +48,7 @@ enum QkFlags {
                                  (bfloat16 rounding of x and y is four orders of magnitude coarser) */
     QK_SINGLE_TABLE = 16u     /* frozen preacts (QK_PREACT_TRAINABLE off): do not build the second per-edge table
                                  that the angle-addition forward reads; the generic forward kernel runs instead
-                                 (about a fifth slower there) and qk_tables_bytes() is halved. For callers short
+                                 (about a fifth slower there) and qk_tables_bytes() is nearly halved. For callers short
                                  of scratch; qk_pz_forward_noalloc sets it by itself when that makes a layer fit */
 };
 
