@@ -124,10 +124,12 @@ __global__ void __launch_bounds__(kPrepThreads) prep_kernel(PrepArgs a) {
 
 // Block = 32 input columns (one lane each) x `blockDim.y` tile slices. Every slice adds the per-tile
 // partials t = slice, slice + slices, ... of each accumulator row; slice 0 then adds the slice sums in
-// order and writes the gradients. Fixed order throughout: run-to-run bitwise reproducible.
+// order and writes the gradients. Fixed order throughout: run-to-run bitwise reproducible. The sums across
+// tiles run in double (the kernel is bound by reading the partials, not by these adds): near a minimum the
+// batch sum cancels to a small value, and optimisers that difference gradients (LBFGS) feel its rounding.
 __global__ void finish_grads_kernel(FinishArgs a) {
     // [slices][nacc + 2][32]; the extra rows are the base-term kernel's partials and the column sums of grad_y
-    extern __shared__ float part[];
+    extern __shared__ double part[];
     const int lane = threadIdx.x, slice = threadIdx.y, slices = blockDim.y;
     const int i = blockIdx.x * kWarp + lane;  // < ipad
     const int o = blockIdx.y;
@@ -137,23 +139,23 @@ __global__ void finish_grads_kernel(FinishArgs a) {
     const float* p0 = a.partials + ((size_t)o * nacc) * a.ipad + i;
     for (int k = 0; k < nacc; ++k) {
         const float* p = p0 + (size_t)k * a.ipad;
-        float s = 0.f;
-        for (int t = slice; t < a.ntiles; t += slices) s += p[(size_t)t * tile_stride];
+        double s = 0.0;
+        for (int t = slice; t < a.ntiles; t += slices) s += (double)p[(size_t)t * tile_stride];
         part[(slice * nrow + k) * kWarp + lane] = s;
     }
     {
-        float s = 0.f;
+        double s = 0.0;
         if (a.base_partials) {
             const float* bp = a.base_partials + (size_t)o * a.ipad + i;
-            for (int t = slice; t < a.base_tiles; t += slices) s += bp[(size_t)t * a.out_dim * a.ipad];
+            for (int t = slice; t < a.base_tiles; t += slices) s += (double)bp[(size_t)t * a.out_dim * a.ipad];
         }
         part[(slice * nrow + nacc) * kWarp + lane] = s;
     }
     {
         // sum_b grad_y[b,o] from the per-tile column sums (the same value in every lane)
-        float s = 0.f;
+        double s = 0.0;
         if (a.colpart)
-            for (int t = slice; t < a.ntiles; t += slices) s += a.colpart[(size_t)t * a.out_dim + o];
+            for (int t = slice; t < a.ntiles; t += slices) s += (double)a.colpart[(size_t)t * a.out_dim + o];
         part[(slice * nrow + nacc + 1) * kWarp + lane] = s;
     }
     __syncthreads();
@@ -162,9 +164,9 @@ __global__ void finish_grads_kernel(FinishArgs a) {
     const bool ptr = (a.flags & QK_PREACT_TRAINABLE) != 0 || a.ansatz == QK_ANSATZ_RPZ;
     const bool use_pb = (a.flags & QK_USE_POSTACT_BIAS) != 0 && a.postb != nullptr;
     auto total = [&](int k) {
-        float s = 0.f;
+        double s = 0.0;
         for (int w = 0; w < slices; ++w) s += part[(w * nrow + k) * kWarp + lane];
-        return s;
+        return (float)s;
     };
     if (a.ansatz == QK_ANSATZ_REAL) {
         // d alpha / d theta_l = -1, / d pb_l = 1, / d pw_l = x for every layer l
@@ -269,10 +271,10 @@ cudaError_t launch_finish(const FinishArgs& a, cudaStream_t st) {
     // as many tile slices as there are tiles to share out, within 48 KB of shared memory
     int slices = 8;
     const int most_tiles = a.ntiles > a.base_tiles ? a.ntiles : a.base_tiles;
-    while (slices > 1 && (slices / 2 >= most_tiles || (size_t)slices * (a.nacc + 2) * kWarp * sizeof(float) > 48 * 1024))
+    while (slices > 1 && (slices / 2 >= most_tiles || (size_t)slices * (a.nacc + 2) * kWarp * sizeof(double) > 48 * 1024))
         slices /= 2;
     dim3 grid(a.ipad / kWarp, a.out_dim), block(kWarp, slices);
-    finish_grads_kernel<<<grid, block, (size_t)slices * (a.nacc + 2) * kWarp * sizeof(float), st>>>(a);
+    finish_grads_kernel<<<grid, block, (size_t)slices * (a.nacc + 2) * kWarp * sizeof(double), st>>>(a);
     return cudaPeekAtLastError();
 }
 
