@@ -484,9 +484,11 @@ class Run:
         """
         for _ in range(max(warmup, 3)):
             step(lambda: None)
-        self.sync_all()
         evs = [[self.event() for _ in range(marks + 2)] for _ in range(steps)]
+        # the sampler starts (NVML initialisation, tens of milliseconds and not the same on every rank) before the
+        # barrier, so that the ranks leave the barrier straight into the first timed step
         with ClockSampler(self.local_rank) as clocks:
+            self.sync_all()
             wall0 = time.perf_counter()
             for k in range(steps):
                 self.flush.zero_()
