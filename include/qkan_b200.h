@@ -127,7 +127,7 @@ int qk_pz_backward(const QkDesc* desc, const void* x, const float* theta,
  * The same layer step with its set-up hoisted out, four launches in all (prepare, forward, backward, finish).
  *
  * qk_pz_forward and qk_pz_backward each begin with a set-up kernel that turns the parameters into per-edge
- * constants (sin/cos of theta, merged phases, postact_weights * mask, the folded bias vector): work the
+ * constants (sin/cos of theta, merged phases, postact_weights * mask, base_weight * mask, the folded bias vector): work the
  * reference redoes inside every CTA (src/qkan/csrc/cute_kernels.cu:96-140, its shared-memory trig cache).
  * A caller that runs forward and backward with unchanged parameters - every training step does - can build
  * that state once with qk_pz_prepare into a buffer of qk_tables_bytes() bytes (depends on in_dim, out_dim,
