@@ -137,6 +137,8 @@ __global__ void finish_grads_kernel(FinishArgs a) {
     const int nacc = a.nacc, nrow = a.nacc + 2;
     const size_t tile_stride = (size_t)a.out_dim * nacc * a.ipad;
     const float* p0 = a.partials + ((size_t)o * nacc) * a.ipad + i;
+    // one accumulator row after the other (four rows at a time, i.e. four times the loads in flight per thread,
+    // measured TWICE as slow at 65536 x 256 -> 256: 0.44 against 0.21 ms)
     for (int k = 0; k < nacc; ++k) {
         const float* p = p0 + (size_t)k * a.ipad;
         double s = 0.0;
@@ -268,8 +270,9 @@ cudaError_t launch_prep(const PrepArgs& a, cudaStream_t st) {
 }
 
 cudaError_t launch_finish(const FinishArgs& a, cudaStream_t st) {
-    // as many tile slices as there are tiles to share out, within 48 KB of shared memory
-    int slices = 8;
+    // as many tile slices as there are tiles to share out, within 48 KB of shared memory; a grid that leaves SMs
+    // idle anyway (narrow layers) takes 16 slices, i.e. half as long a chain of dependent loads per thread
+    int slices = (long)(a.ipad / kWarp) * a.out_dim < 2 * 148 ? 16 : 8;
     const int most_tiles = a.ntiles > a.base_tiles ? a.ntiles : a.base_tiles;
     while (slices > 1 && (slices / 2 >= most_tiles || (size_t)slices * (a.nacc + 2) * kWarp * sizeof(double) > 48 * 1024))
         slices /= 2;
