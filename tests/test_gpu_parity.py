@@ -311,8 +311,10 @@ def test_seeded_random_shapes_and_flags_vs_oracle():
 
 
 @pytest.mark.parametrize("B,I,O,io_dtype", [(19205, 202, 70, torch.float32), (19200, 200, 130, torch.float32),
-                                            (19200, 200, 130, torch.bfloat16), (300, 37, 9, torch.float32)],
-                         ids=["ragged-scalar-columns", "two-output-tiles", "bf16", "small-tiles"])
+                                            (19200, 200, 130, torch.bfloat16), (300, 37, 9, torch.float32),
+                                            (19200, 200, 128, torch.bfloat16), (300, 40, 12, torch.bfloat16)],
+                         ids=["ragged-scalar-columns", "two-output-tiles", "bf16", "small-tiles",
+                              "bf16-four-outputs-at-a-time", "bf16-small-tiles"])
 def test_base_term_backward_products(B, I, O, io_dtype):
     """The base term's two matrix products (grad_x share and grad_base_weight) at shapes that use the 128-wide
     tiles, several slabs of batch rows, ragged tile edges and both the four-column and the single-column
