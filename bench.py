@@ -619,7 +619,7 @@ def run_layer(run: Run):
         hy = torch.empty((rows, OUT_DIM), dtype=torch.float32).pin_memory()
         hgx = torch.empty((rows, IN_DIM), dtype=torch.float32).pin_memory()
         hgrads = torch.empty(bucket.flat.numel(), dtype=torch.float32).pin_memory()
-        e2e_steps = max(3, min(args.steps, 10))
+        e2e_steps = max(3, min(args.steps, 20))
         pipe = HostLayerPipeline(rows, IN_DIM, OUT_DIM, REPS, dev, n_chunks=args.e2e_chunks)
         dev_params = {k: t[k] for k in ("theta", "pw", "pb", "postw", "postb")}
         for _ in range(2):
